@@ -1,0 +1,8 @@
+// placeholder until the fused attention kernel lands
+#include "common.cuh"
+extern "C" size_t sparta_attn_fwd_workspace_bytes(int, int, int, int, int) { return 0; }
+extern "C" int sparta_attn_fwd(const void*, const void*, const void*, void*, const int32_t*,
+                               const int32_t*, const int32_t*, const uint8_t*, float, int, int, int,
+                               int, int, int, float*, int32_t*, void*, size_t, void*) {
+  return SPARTA_ERR_UNSUPPORTED;
+}

@@ -1,0 +1,302 @@
+// Dense uint8 mask -> BCSR / BCSC / BCSRC block indexes in ONE launch.
+//
+// Phase 1 (every CTA): warps stream strips of the mask (BH rows x a 512-byte column segment) with
+// 16-byte loads, OR-reduce each BH x BW block in registers and store one occupancy byte per block.
+// Phase 2 (the last CTA of each mask to finish, found with an atomic ticket -- no spinning): counts
+// per block row, a block-wide prefix sum into row_ptr and an ordered compaction into the packed
+// index array, so entries come out in ascending column order within a row.
+//
+// Replaces bcs_index_1 / bcs_index_2 + torch.cumsum + .item()
+// (sparta/tesa/templates/block_compressed.cu.j2:67-170, sparta/tesa/block_compressed.py:242-309).
+#include "common.cuh"
+
+namespace sparta {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+struct BcsParams {
+  const uint8_t* mask;
+  int n_masks, H, W, BH, BW, R, Cn;
+  int want_bcsr, want_bcsc;
+  int32_t* row_ptr;
+  int32_t* bcsr_idx;
+  int32_t* col_ptr;
+  void* bcsc_idx;
+  long long idx_capacity;
+  int32_t* nnz;
+  int32_t* uniform;
+  uint8_t* occ;        // [n_masks, R, Cn]  bit0 = block kept, bit1 = block has a zero byte
+  int32_t* rank;       // [n_masks, R, Cn]  BCSR position of kept blocks (only when both formats)
+  unsigned* counters;  // [n_masks] tickets, zero between calls
+  int seg_w;           // bytes of one mask row a warp covers per unit
+  int segs;            // units per block row
+  int units_per_mask;
+};
+
+// 0x80 in every byte of w that is zero
+__device__ __forceinline__ uint32_t zero_bytes(uint32_t w) {
+  return (w - 0x01010101u) & ~w & 0x80808080u;
+}
+
+// In-place inclusive scan of p[1..n] (p[0] must be 0) by one CTA of kThreads threads.
+__device__ void block_scan_inplace(int32_t* p, int n, int32_t* s_part) {
+  const int tid = threadIdx.x;
+  const int chunk = (n + kThreads - 1) / kThreads;
+  const int lo = min(n, tid * chunk), hi = min(n, lo + chunk);
+  int sum = 0;
+  for (int i = lo; i < hi; ++i) sum += p[i + 1];
+  s_part[tid] = sum;
+  __syncthreads();
+  // Hillis-Steele over 256 partials
+  for (int off = 1; off < kThreads; off <<= 1) {
+    int v = tid >= off ? s_part[tid - off] : 0;
+    __syncthreads();
+    s_part[tid] += v;
+    __syncthreads();
+  }
+  int run = s_part[tid] - sum;  // exclusive prefix of this thread's chunk
+  for (int i = lo; i < hi; ++i) {
+    run += p[i + 1];
+    p[i + 1] = run;
+  }
+  __syncthreads();
+}
+
+template <int VW>
+__global__ void __launch_bounds__(kThreads) bcs_build_kernel(BcsParams p) {
+  constexpr int NWORD = VW / 4;
+  const int b = blockIdx.y;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const uint8_t* mask = p.mask + (size_t)b * p.H * p.W;
+  uint8_t* occ = p.occ + (size_t)b * p.R * p.Cn;
+
+  // ---------------- phase 1: block occupancy ----------------
+  const int nwarps = gridDim.x * kWarps;
+  for (int u = blockIdx.x * kWarps + warp; u < p.units_per_mask; u += nwarps) {
+    const int r = u / p.segs;
+    const int col0 = (u - r * p.segs) * p.seg_w;
+    uint32_t any[NWORD], zer[NWORD];
+#pragma unroll
+    for (int i = 0; i < NWORD; ++i) any[i] = zer[i] = 0;
+    const uint8_t* row0 = mask + (size_t)r * p.BH * p.W;
+    for (int c = col0 + lane * VW; c < col0 + p.seg_w; c += 32 * VW) {
+      if (c < p.W) {
+        const uint8_t* src = row0 + c;
+        for (int y = 0; y < p.BH; y += 4) {  // BH is a multiple of 4: four loads in flight
+          if constexpr (VW == 16) {
+            uint4 v0 = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(y + 0) * p.W));
+            uint4 v1 = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(y + 1) * p.W));
+            uint4 v2 = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(y + 2) * p.W));
+            uint4 v3 = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(y + 3) * p.W));
+            any[0] |= v0.x | v1.x | v2.x | v3.x;
+            any[1] |= v0.y | v1.y | v2.y | v3.y;
+            any[2] |= v0.z | v1.z | v2.z | v3.z;
+            any[3] |= v0.w | v1.w | v2.w | v3.w;
+            zer[0] |= zero_bytes(v0.x) | zero_bytes(v1.x) | zero_bytes(v2.x) | zero_bytes(v3.x);
+            zer[1] |= zero_bytes(v0.y) | zero_bytes(v1.y) | zero_bytes(v2.y) | zero_bytes(v3.y);
+            zer[2] |= zero_bytes(v0.z) | zero_bytes(v1.z) | zero_bytes(v2.z) | zero_bytes(v3.z);
+            zer[3] |= zero_bytes(v0.w) | zero_bytes(v1.w) | zero_bytes(v2.w) | zero_bytes(v3.w);
+          } else {
+            uint32_t v0 = __ldg(reinterpret_cast<const uint32_t*>(src + (size_t)(y + 0) * p.W));
+            uint32_t v1 = __ldg(reinterpret_cast<const uint32_t*>(src + (size_t)(y + 1) * p.W));
+            uint32_t v2 = __ldg(reinterpret_cast<const uint32_t*>(src + (size_t)(y + 2) * p.W));
+            uint32_t v3 = __ldg(reinterpret_cast<const uint32_t*>(src + (size_t)(y + 3) * p.W));
+            any[0] |= v0 | v1 | v2 | v3;
+            zer[0] |= zero_bytes(v0) | zero_bytes(v1) | zero_bytes(v2) | zero_bytes(v3);
+          }
+        }
+      }
+    }
+    const int c_lane = col0 + lane * VW;  // first column of this lane's (first) chunk
+    if (p.BW >= VW) {
+      uint32_t a = 0, z = 0;
+#pragma unroll
+      for (int i = 0; i < NWORD; ++i) { a |= any[i]; z |= zer[i]; }
+      const int g = min(32, p.BW / VW);  // lanes per block
+      for (int off = 1; off < g; off <<= 1) {
+        a |= __shfl_xor_sync(0xffffffffu, a, off);
+        z |= __shfl_xor_sync(0xffffffffu, z, off);
+      }
+      const int cb = c_lane / p.BW;
+      if ((lane & (g - 1)) == 0 && cb < p.Cn)
+        occ[(size_t)r * p.Cn + cb] = a ? (z ? 3 : 1) : 0;
+    } else {
+      // several blocks per lane (VW == 16, BW in {4, 8})
+      const int words_per_block = p.BW / 4;
+      for (int w = 0; w < NWORD; w += words_per_block) {
+        uint32_t a = any[w], z = zer[w];
+        if (words_per_block == 2 && w + 1 < NWORD) { a |= any[w + 1]; z |= zer[w + 1]; }
+        const int cb = (c_lane + w * 4) / p.BW;
+        if (cb < p.Cn) occ[(size_t)r * p.Cn + cb] = a ? (z ? 3 : 1) : 0;
+      }
+    }
+  }
+
+  // ---------------- ticket: is this the last CTA of mask b? ----------------
+  __shared__ int s_last;
+  __shared__ int32_t s_part[kThreads];
+  __shared__ int s_nonuniform;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned ticket = atomicAdd(&p.counters[b], 1u);
+    s_last = (ticket == gridDim.x - 1);
+    s_nonuniform = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+
+  // ---------------- phase 2: scan + ordered compaction ----------------
+  const int R = p.R, Cn = p.Cn;
+  int32_t* rank = p.rank ? p.rank + (size_t)b * R * Cn : nullptr;
+  int nonuni = 0;
+  if (p.want_bcsr) {
+    int32_t* row_ptr = p.row_ptr + (size_t)b * (R + 1);
+    int32_t* out = p.bcsr_idx + (size_t)b * p.idx_capacity;
+    if (threadIdx.x == 0) row_ptr[0] = 0;
+    for (int r = warp; r < R; r += kWarps) {
+      int cnt = 0;
+      for (int c = lane; c < Cn; c += 32) {
+        const int o = __ldcg(&occ[(size_t)r * Cn + c]);
+        cnt += o & 1;
+        nonuni |= o & 2;
+      }
+      cnt = warp_sum_int(cnt);
+      if (lane == 0) row_ptr[r + 1] = cnt;
+    }
+    __syncthreads();
+    block_scan_inplace(row_ptr, R, s_part);
+    for (int r = warp; r < R; r += kWarps) {
+      int off = row_ptr[r];
+      for (int c0 = 0; c0 < Cn; c0 += 32) {
+        const int c = c0 + lane;
+        const int f = (c < Cn) ? (__ldcg(&occ[(size_t)r * Cn + c]) & 1) : 0;
+        const unsigned bal = __ballot_sync(0xffffffffu, f);
+        if (f) {
+          const int pos = off + __popc(bal & ((1u << lane) - 1u));
+          if (pos < p.idx_capacity) out[pos] = (r << 16) | c;
+          if (rank) rank[(size_t)r * Cn + c] = pos;
+        }
+        off += __popc(bal);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) p.nnz[b] = row_ptr[R];
+  }
+  if (p.want_bcsc) {
+    int32_t* col_ptr = p.col_ptr + (size_t)b * (Cn + 1);
+    if (threadIdx.x == 0) col_ptr[0] = 0;
+    for (int c = threadIdx.x; c < Cn; c += kThreads) {
+      int cnt = 0;
+      for (int r = 0; r < R; ++r) {
+        const int o = __ldcg(&occ[(size_t)r * Cn + c]);
+        cnt += o & 1;
+        nonuni |= o & 2;
+      }
+      col_ptr[c + 1] = cnt;
+    }
+    __syncthreads();
+    block_scan_inplace(col_ptr, Cn, s_part);
+    const bool both = p.want_bcsr != 0;
+    int32_t* out32 = reinterpret_cast<int32_t*>(p.bcsc_idx) + (size_t)b * p.idx_capacity;
+    long long* out64 = reinterpret_cast<long long*>(p.bcsc_idx) + (size_t)b * p.idx_capacity;
+    for (int c = threadIdx.x; c < Cn; c += kThreads) {
+      int pos = col_ptr[c];
+      for (int r = 0; r < R; ++r) {
+        if (__ldcg(&occ[(size_t)r * Cn + c]) & 1) {
+          if (pos < p.idx_capacity) {
+            if (both)
+              out64[pos] = ((long long)rank[(size_t)r * Cn + c] << 32) | (long long)((c << 16) | r);
+            else
+              out32[pos] = (c << 16) | r;
+          }
+          ++pos;
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !p.want_bcsr) p.nnz[b] = col_ptr[Cn];
+  }
+  if (nonuni) s_nonuniform = 1;  // benign race: every writer stores 1
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (p.uniform) p.uniform[b] = s_nonuniform ? 0 : 1;
+    p.counters[b] = 0;  // leave the ticket ready for the next call
+  }
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+}  // namespace sparta
+
+using namespace sparta;
+
+extern "C" size_t sparta_bcs_build_workspace_bytes(int n_masks, int H, int W, int BH, int BW) {
+  if (n_masks <= 0 || H <= 0 || W <= 0 || BH <= 0 || BW <= 0) return 0;
+  const size_t blocks = (size_t)n_masks * (H / BH) * (W / BW);
+  // occupancy bytes + BCSR ranks (int32) + tickets
+  return align_up(blocks, 256) + align_up(blocks * 4, 256) + align_up((size_t)n_masks * 4, 256);
+}
+
+extern "C" int sparta_bcs_build(const uint8_t* mask, int n_masks, int H, int W, int BH, int BW,
+                                int want_bcsr, int want_bcsc, int32_t* row_ptr, int32_t* bcsr_idx,
+                                int32_t* col_ptr, void* bcsc_idx, int64_t idx_capacity, int32_t* nnz,
+                                int32_t* uniform, int32_t* h_nnz, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+  if (!mask || !nnz || n_masks <= 0 || H <= 0 || W <= 0) return SPARTA_ERR_BAD_ARG;
+  if (!want_bcsr && !want_bcsc) return SPARTA_ERR_BAD_ARG;
+  if (want_bcsr && (!row_ptr || !bcsr_idx)) return SPARTA_ERR_BAD_ARG;
+  if (want_bcsc && (!col_ptr || !bcsc_idx)) return SPARTA_ERR_BAD_ARG;
+  if (!valid_bcs_block(BH) || !valid_bcs_block(BW)) return SPARTA_ERR_SHAPE;
+  if (H % BH || W % BW) return SPARTA_ERR_SHAPE;
+  const int R = H / BH, Cn = W / BW;
+  if (R > 32767 || Cn > 65535 || idx_capacity <= 0) return SPARTA_ERR_SHAPE;  // 16-bit packing
+  if (n_masks > 65535) return SPARTA_ERR_SHAPE;
+  if (!workspace || workspace_bytes < sparta_bcs_build_workspace_bytes(n_masks, H, W, BH, BW))
+    return SPARTA_ERR_WORKSPACE;
+  if (!aligned(workspace, 256) || !aligned(mask, 4)) return SPARTA_ERR_ALIGN;
+
+  const size_t blocks = (size_t)n_masks * R * Cn;
+  BcsParams p;
+  p.mask = mask;
+  p.n_masks = n_masks; p.H = H; p.W = W; p.BH = BH; p.BW = BW; p.R = R; p.Cn = Cn;
+  p.want_bcsr = want_bcsr; p.want_bcsc = want_bcsc;
+  p.row_ptr = row_ptr; p.bcsr_idx = bcsr_idx; p.col_ptr = col_ptr; p.bcsc_idx = bcsc_idx;
+  p.idx_capacity = idx_capacity;
+  p.nnz = nnz; p.uniform = uniform;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  p.occ = ws;
+  p.rank = (want_bcsr && want_bcsc) ? reinterpret_cast<int32_t*>(ws + align_up(blocks, 256)) : nullptr;
+  p.counters = reinterpret_cast<unsigned*>(ws + align_up(blocks, 256) + align_up(blocks * 4, 256));
+
+  const bool vec16 = (W % 16 == 0) && aligned(mask, 16);
+  const int vw = vec16 ? 16 : 4;
+  p.seg_w = (32 * vw > BW) ? 32 * vw : BW;
+  p.segs = (W + p.seg_w - 1) / p.seg_w;
+  p.units_per_mask = R * p.segs;
+
+  // spread the units of all masks over every resident warp slot of the GPU (148 SMs x 64 warps)
+  const long long total_units = (long long)n_masks * p.units_per_mask;
+  const long long warp_slots = (long long)kNumSMs * 64;
+  const int units_per_warp = (int)((total_units + warp_slots - 1) / warp_slots);
+  int ctas = (p.units_per_mask + kWarps * units_per_warp - 1) / (kWarps * units_per_warp);
+  if (ctas < 1) ctas = 1;
+  dim3 grid(ctas, n_masks), block(kThreads);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (vec16)
+    bcs_build_kernel<16><<<grid, block, 0, st>>>(p);
+  else
+    bcs_build_kernel<4><<<grid, block, 0, st>>>(p);
+  int rc = launch_status();
+  if (rc != SPARTA_OK) return rc;
+  if (h_nnz) {
+    cudaError_t e = cudaMemcpyAsync(h_nnz, nnz, sizeof(int32_t) * n_masks, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  return SPARTA_OK;
+}

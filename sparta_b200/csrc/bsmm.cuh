@@ -1,0 +1,34 @@
+// Internal parameter block shared by the block-sparse matmul kernels.
+#pragma once
+
+#include "common.cuh"
+
+namespace sparta {
+
+enum BsmmMode { MODE_SDD = 0, MODE_DSD = 1, MODE_DDS = 2 };
+
+struct BsmmParams {
+  const void* A;
+  const void* B;
+  const void* bias;
+  void* C;
+  const int32_t* ptr;
+  const void* idx;
+  const int32_t* nnz;
+  int mode;
+  int batch, M, K, N;
+  int BM, BK, BN;
+  int trans_a, trans_b, compressed, idx_is_64;
+  int dtype;
+  int n_index_sets;
+  long long ptr_stride, idx_stride, val_stride_blocks, grid_blocks_hint;
+};
+
+// FMA kernel: every layout.  Returns a status code of sparta_b200.h.
+int bsmm_simt(const BsmmParams& p, cudaStream_t st);
+
+// tcgen05 kernels: return SPARTA_ERR_UNSUPPORTED when the configuration is outside their coverage.
+bool bsmm_tc_supported(const BsmmParams& p);
+int bsmm_tc(const BsmmParams& p, cudaStream_t st);
+
+}  // namespace sparta

@@ -1,0 +1,142 @@
+// Masked softmax over the kept blocks of each row: one warp per matrix row, one online
+// (max, sum) pass followed by one write pass, so x is read from HBM once (the second read hits L1/L2).
+//
+// Replaces sparta_sparse_softmax_forward.cuh.j2 / sparta_sparse_softmax_backward.cuh.j2
+// (sparta/specializer/kernels/templates/): three global passes plus a per-thread index list there.
+#include "common.cuh"
+
+namespace sparta {
+namespace {
+
+struct SmParams {
+  const void* x;      // fwd: x      bwd: dy
+  const void* y_in;   // bwd: y
+  void* out;          // fwd: y      bwd: dx
+  const int32_t* row_ptr;
+  const int32_t* idx;
+  const int32_t* nnz;
+  const uint8_t* mask;
+  float scale;
+  int H, W, BH, BW, compressed;
+  long long val_stride_blocks;
+};
+
+// element offset of (block t, row y inside the block, column x inside the block)
+__device__ __forceinline__ long long elem_off(const SmParams& p, int t, int row, int y, int x) {
+  if (p.compressed) return ((long long)t * p.BH + y) * p.BW + x;
+  return (long long)row * p.W + (long long)(p.idx[t] & 0xffff) * p.BW + x;
+}
+
+template <typename T, bool BACKWARD>
+__global__ void __launch_bounds__(256) softmax_kernel(SmParams p) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= p.H) return;
+  const long long bstride = p.compressed ? p.val_stride_blocks * p.BH * p.BW : (long long)p.H * p.W;
+  const T* x = static_cast<const T*>(p.x) + (long long)blockIdx.y * bstride;
+  T* out = static_cast<T*>(p.out) + (long long)blockIdx.y * bstride;
+  const int br = row / p.BH, y = row - br * p.BH;
+  const int t0 = p.row_ptr[br], t1 = p.row_ptr[br + 1];
+  const int n = (t1 - t0) * p.BW;
+  const int shift = __ffs(p.BW) - 1;  // BW is a power of two
+
+  if (!BACKWARD) {
+    float m = -INFINITY, s = 0.f;
+    for (int j = lane; j < n; j += 32) {
+      const long long o = elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1));
+      if (p.mask && !p.mask[o]) continue;
+      const float v = to_float(x[o]) * p.scale;
+      if (v > m) { s = s * expf(m - v) + 1.f; m = v; }
+      else s += expf(v - m);
+    }
+    const float mw = warp_max(m);
+    s = (m == -INFINITY) ? 0.f : s * expf(m - mw);
+    s = warp_sum(s);
+    const float inv = s > 0.f ? 1.f / s : 0.f;
+    for (int j = lane; j < n; j += 32) {
+      const long long o = elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1));
+      float r = 0.f;
+      if (!p.mask || p.mask[o]) r = expf(to_float(x[o]) * p.scale - mw) * inv;
+      out[o] = from_float<T>(r);
+    }
+  } else {
+    const T* yv = static_cast<const T*>(p.y_in) + (long long)blockIdx.y * bstride;
+    float dot = 0.f;
+    for (int j = lane; j < n; j += 32) {
+      const long long o = elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1));
+      if (p.mask && !p.mask[o]) continue;
+      dot += to_float(x[o]) * to_float(yv[o]);
+    }
+    dot = warp_sum(dot);
+    for (int j = lane; j < n; j += 32) {
+      const long long o = elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1));
+      float r = 0.f;
+      if (!p.mask || p.mask[o]) {
+        const float yy = to_float(yv[o]);
+        r = (to_float(x[o]) * yy - yy * dot) * p.scale;
+      }
+      out[o] = from_float<T>(r);
+    }
+  }
+}
+
+template <bool BACKWARD>
+int launch(const SmParams& p, int batch, int dtype, cudaStream_t st) {
+  dim3 grid((p.H + 7) / 8, batch), block(256);
+  switch (dtype) {
+    case SPARTA_F32: softmax_kernel<float, BACKWARD><<<grid, block, 0, st>>>(p); break;
+    case SPARTA_F16: softmax_kernel<__half, BACKWARD><<<grid, block, 0, st>>>(p); break;
+    case SPARTA_BF16: softmax_kernel<__nv_bfloat16, BACKWARD><<<grid, block, 0, st>>>(p); break;
+    default: return SPARTA_ERR_BAD_ARG;
+  }
+  return launch_status();
+}
+
+int check(const void* a, const void* b, const int32_t* row_ptr, const int32_t* idx, const int32_t* nnz,
+          int batch, int H, int W, int BH, int BW, int compressed, int64_t vsb) {
+  if (!a || !b || !row_ptr || !idx || !nnz || batch <= 0 || H <= 0 || W <= 0) return SPARTA_ERR_BAD_ARG;
+  if (!valid_bcs_block(BH) || !valid_bcs_block(BW) || H % BH || W % BW) return SPARTA_ERR_SHAPE;
+  if (batch > 65535) return SPARTA_ERR_SHAPE;
+  if (compressed && vsb < 0) return SPARTA_ERR_BAD_ARG;
+  return SPARTA_OK;
+}
+
+}  // namespace
+}  // namespace sparta
+
+using namespace sparta;
+
+extern "C" int sparta_softmax_fwd(const void* x, void* y, const int32_t* row_ptr,
+                                  const int32_t* bcsr_idx, const int32_t* nnz, const uint8_t* mask,
+                                  float scale, int batch, int H, int W, int BH, int BW, int compressed,
+                                  int dtype, int64_t val_stride_blocks, void* stream) {
+  int rc = check(x, y, row_ptr, bcsr_idx, nnz, batch, H, W, BH, BW, compressed, val_stride_blocks);
+  if (rc != SPARTA_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!compressed) {  // dropped blocks of the dense-shaped output must read 0
+    const size_t esz = dtype == SPARTA_F32 ? 4 : 2;
+    cudaError_t e = cudaMemsetAsync(y, 0, (size_t)batch * H * W * esz, st);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  SmParams p{x, nullptr, y, row_ptr, bcsr_idx, nnz, mask, scale, H, W, BH, BW, compressed,
+             (long long)val_stride_blocks};
+  return launch<false>(p, batch, dtype, st);
+}
+
+extern "C" int sparta_softmax_bwd(const void* dy, const void* y, void* dx, const int32_t* row_ptr,
+                                  const int32_t* bcsr_idx, const int32_t* nnz, const uint8_t* mask,
+                                  float scale, int batch, int H, int W, int BH, int BW, int compressed,
+                                  int dtype, int64_t val_stride_blocks, void* stream) {
+  int rc = check(dy, dx, row_ptr, bcsr_idx, nnz, batch, H, W, BH, BW, compressed, val_stride_blocks);
+  if (rc != SPARTA_OK) return rc;
+  if (!y) return SPARTA_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!compressed) {
+    const size_t esz = dtype == SPARTA_F32 ? 4 : 2;
+    cudaError_t e = cudaMemsetAsync(dx, 0, (size_t)batch * H * W * esz, st);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  SmParams p{dy, y, dx, row_ptr, bcsr_idx, nnz, mask, scale, H, W, BH, BW, compressed,
+             (long long)val_stride_blocks};
+  return launch<true>(p, batch, dtype, st);
+}

@@ -1,0 +1,89 @@
+"""Generate the golden vectors of ``tests/golden`` from the reference's own CPU-capable code.
+
+Run once in a container that holds the reference checkout (it is not needed afterwards):
+
+    python tests/golden/make_golden.py /path/to/SparTA
+
+``import sparta`` fails without pycuda and the compiled extensions, so the three modules that only
+need torch / numpy are loaded by file path: ``sparta/testing/math.py``, ``sparta/testing/mask.py``
+and, from ``test/unit/test_tesa.py``, the ``reduce_mask_ref`` helper (extracted with ``ast`` because
+the test module itself imports ``sparta``).  Outputs are small ``.npz`` files.
+"""
+import ast
+import importlib.util
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def load_by_path(name, path):
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def load_function(path, func_name):
+    tree = ast.parse(open(path).read())
+    node = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == func_name)
+    ns = {'torch': torch}
+    exec(compile(ast.Module(body=[node], type_ignores=[]), path, 'exec'), ns)
+    return ns[func_name]
+
+
+def main(ref_root):
+    math_ref = load_by_path('ref_math', os.path.join(ref_root, 'sparta/testing/math.py'))
+    mask_ref = load_by_path('ref_mask', os.path.join(ref_root, 'sparta/testing/mask.py'))
+    reduce_mask_ref = load_function(os.path.join(ref_root, 'test/unit/test_tesa.py'), 'reduce_mask_ref')
+
+    # ---- masks: the reference generator on the CPU, seeded through the global RNG ----
+    out = {}
+    for i, (shape, block, sparsity, seed) in enumerate([
+        ((256, 192), (1, 1), 0.99, 2023),
+        ((128, 256), (8, 8), 0.9, 2022),
+        ((64, 64), (32, 32), 0.5, 7),
+    ]):
+        torch.manual_seed(seed)
+        m = mask_ref.block_mask(shape, block=block, sparsity=sparsity, device='cpu')
+        out[f'mask{i}'] = m.numpy()
+        out[f'mask{i}_args'] = np.array([*shape, *block, int(sparsity * 10000), seed])
+    np.savez_compressed(os.path.join(HERE, 'masks.npz'), **out)
+
+    # ---- block occupancy (reduce_mask_ref) for the test_tesa.py block-size grid ----
+    torch.manual_seed(2023)
+    mask = mask_ref.block_mask((256, 384), sparsity=0.995, device='cpu')
+    out = {'mask': mask.numpy()}
+    for BH in [4, 8, 16, 32, 64, 128]:
+        for BW in [4, 8, 16, 32, 64, 128]:
+            out[f'occ_{BH}_{BW}'] = reduce_mask_ref(mask, BH, BW).numpy()
+    np.savez_compressed(os.path.join(HERE, 'tesa.npz'), **out)
+
+    # ---- softmax forward / backward and attention ----
+    torch.manual_seed(2022)
+    H, W = 64, 128
+    x = torch.rand((2, H, W))
+    grad = torch.rand((2, H, W))
+    mask = mask_ref.block_mask((H, W), block=(8, 8), sparsity=0.9, device='cpu')
+    mask[5 * 8:6 * 8] = 0  # make some rows fully masked
+    T = float(np.sqrt(W))
+    y = math_ref.sparse_softmax_forward_reference(x, mask, T)
+    dx = math_ref.sparse_softmax_backward_reference(grad, y, mask, T)
+    q = torch.rand((2, 64, 32))
+    k = torch.rand((2, 96, 32))
+    v = torch.rand((2, 96, 32))
+    amask = mask_ref.block_mask((64, 96), block=(8, 8), sparsity=0.8, device='cpu')
+    o = math_ref.sparse_multi_head_attention_reference(q, k, v, amask)
+    np.savez_compressed(
+        os.path.join(HERE, 'softmax_attention.npz'),
+        x=x.numpy(), grad=grad.numpy(), mask=mask.numpy(), T=np.float64(T), y=y.numpy(), dx=dx.numpy(),
+        q=q.numpy(), k=k.numpy(), v=v.numpy(), amask=amask.numpy(), o=o.numpy(),
+    )
+    print('golden vectors written to', HERE)
+
+
+if __name__ == '__main__':
+    main(sys.argv[1] if len(sys.argv) > 1 else '/root/reference')
