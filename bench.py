@@ -1,0 +1,416 @@
+"""Benchmark of the block-sparse operator path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
+
+One step = one pass of the hot path over one batch of seeded synthetic input.  The headline workload
+is SparseLinear fp16, x[4096 tokens, 4096] . W[4096, 4096]^T + b with a 32x32-block weight mask at 75 %
+block sparsity (dsd, weight held as BCSR values); metric = TFLOP/s on the FLOPs of the kept blocks.
+With N > 1 every rank runs that workload on its own shard of 4096 token rows (weak scaling, no
+collective on the data path).  Rank 0 prints ONE JSON line.
+
+Extras (rank 0, N = 1): the other sparsities and the dds form, the fused sparse attention forward
+(B4 H16 S4096 D64, ms), the GPU mask -> BCSR conversion of 32 masks of 2048 x 2048 (us, GB/s), that
+conversion plus the dds matmul (dynamic sparsity), and the fp32 README workload.
+
+``--impl reference`` times the reference's own way of computing the same thing on the host cores:
+masked-dense torch (the computation its unit tests compare against), via the oracle.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TOKENS, IN_F, OUT_F, BLOCK = 4096, 4096, 4096, 32
+SPARSITY = 0.75
+
+
+def load_peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {'hbm_gbs': p['hbm_gbs'], 'tflops': p['bf16_tflops'],
+                'tflops_sustained': p.get('bf16_tflops_sustained', p['bf16_tflops']), 'source': 'measured'}
+    return {'hbm_gbs': 6650.0, 'tflops': 1590.0, 'tflops_sustained': 1400.0, 'source': 'fallback'}
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic inputs (seeded on the CPU so that every rank and the CPU baseline see the same bits)
+# ------------------------------------------------------------------------------------------------
+
+def linear_inputs(sparsity, seed=2023, tokens=TOKENS):
+    from oracle import oracle  # input generator shared with the checker; not on the timed path
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((tokens, IN_F), generator=g).half()
+    w = (torch.randn((OUT_F, IN_F), generator=g) * 0.02).half()
+    b = torch.randn((OUT_F,), generator=g).half()
+    mask = oracle.block_mask((OUT_F, IN_F), (BLOCK, BLOCK), sparsity, generator=g)
+    return x, w * mask, b, mask
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+             'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+             'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, device_index):
+        self.index = device_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ['nvidia-smi', f'--query-gpu={self.QUERY}', '--format=csv,noheader,nounits', '-lms', '100',
+                 '-i', str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            f = [s.strip() for s in line.split(',')]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'], f[5:9]):
+                if val.lower().startswith('active'):
+                    reasons.add(name)
+        sm.sort()
+        return {'sm_mhz': sm[len(sm) // 2] if sm else None, 'sm_max_mhz': max(mx) if mx else None,
+                'reasons': sorted(reasons), 'samples': len(sm)}
+
+
+class L2Flusher:
+    """Writes a buffer larger than the 126 MB L2 so that the next step starts cold."""
+
+    def __init__(self, device, nbytes=256 << 20):
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+    def __call__(self):
+        self.buf.fill_(1)
+
+
+def time_steps(fn, steps, warmup, flush, barrier=None):
+    """Per-step CUDA-event timing on the current stream, L2 flushed (untimed) before every step.
+    Returns the summed milliseconds of the ``steps`` timed steps."""
+    for _ in range(warmup):
+        flush()
+        fn()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        flush()
+        starts[i].record()
+        fn()
+        stops[i].record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return sum(s.elapsed_time(e) for s, e in zip(starts, stops))
+
+
+# ------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------
+
+def token_tile():
+    """Token rows per CTA tile of the dsd kernel: 128 for the tcgen05 kernel, 64 for the FMA kernel."""
+    from sparta_b200 import _lib
+    first = _lib.tile_table(_lib.OP_DSD, _lib.F16)[0]
+    return first.block_m if first.impl == _lib.IMPL_TCGEN05 else 64
+
+
+def build_linear(device, sparsity, mode='dsd', tokens=TOKENS):
+    import sparta_b200 as sparta
+    x, w, b, mask = linear_inputs(sparsity, tokens=tokens)
+    dense = torch.nn.Linear(IN_F, OUT_F, device=device, dtype=torch.float16)
+    dense.load_state_dict({'weight': w.to(device), 'bias': b.to(device)})
+    if mode == 'dsd':
+        op = sparta.nn.SparseLinear(dense, weight_mask=mask.to(device))
+        cfg = {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': token_tile(), 'BLOCK_SIZE_K_VALUE': BLOCK,
+               'BLOCK_SIZE_N_VALUE': BLOCK}
+    else:
+        # dds: dense operands, output restricted to the same block pattern over [tokens, out]
+        op = sparta.nn.SparseBatchMatMul(C_mask=mask[:tokens].to(device), transpose_B=True, compressed=True)
+        cfg = {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': BLOCK, 'BLOCK_SIZE_K_VALUE': 64, 'BLOCK_SIZE_N_VALUE': BLOCK}
+    xd = x.to(device)
+    if mode == 'dsd':
+        op.build({'forward:C': cfg}, sample_inputs=[xd])
+        nnz = op.get_sparse_indexes('B').block_nnz
+        fn = lambda: op(xd)
+    else:
+        wd = w.to(device).unsqueeze(0)
+        xd3 = xd.unsqueeze(0)
+        op.build({'forward:C': cfg}, sample_inputs=[xd3, wd])
+        nnz = op.get_sparse_indexes('C').block_nnz
+        fn = lambda: op(xd3, wd)
+    flops = 2.0 * (tokens * BLOCK * BLOCK * nnz if mode == 'dsd' else BLOCK * BLOCK * IN_F * nnz)
+    if mode == 'dsd':
+        bytes_ = 2.0 * (tokens * IN_F + tokens * OUT_F + nnz * BLOCK * BLOCK + OUT_F)
+    else:
+        bytes_ = 2.0 * (tokens * IN_F + OUT_F * IN_F + nnz * BLOCK * BLOCK)
+    return dict(op=op, fn=fn, x=x, w=w, b=b, mask=mask, xd=xd, nnz=nnz, flops=flops, bytes=bytes_)
+
+
+def run_extras(device, peaks, flush):
+    """Secondary measurements (each: 3 warm-ups, 10 timed steps, L2 flushed between steps)."""
+    import sparta_b200 as sparta
+    from oracle import oracle
+    extras = {}
+
+    def timed(fn, steps=10):
+        return time_steps(fn, steps, 3, flush) / steps
+
+    for mode in ('dsd', 'dds'):
+        for sp in (0.75, 0.9, 0.95):
+            if mode == 'dsd' and sp == SPARSITY:
+                continue
+            try:
+                wl = build_linear(device, sp, mode)
+                ms = timed(wl['fn'])
+                tf = wl['flops'] / ms / 1e9
+                extras[f'linear_{mode}_{int(sp * 100)}'] = {
+                    'ms': round(ms, 4), 'nnz_blocks': wl['nnz'], 'tflops': round(tf, 2),
+                    'frac_tensor_peak': round(tf / peaks['tflops'], 4),
+                    'gbs': round(wl['bytes'] / ms / 1e6, 1), 'frac_hbm_peak': round(wl['bytes'] / ms / 1e6 / peaks['hbm_gbs'], 4)}
+                del wl
+            except Exception as e:  # an extra must not take the headline number down
+                extras[f'linear_{mode}_{int(sp * 100)}'] = {'error': repr(e)[:200]}
+
+    # fused sparse attention forward: B4 H16 S4096 D64 fp16, band + global + 5 % random 64x64 blocks
+    try:
+        heads, S, D = 64, 4096, 64
+        g = torch.Generator().manual_seed(2024)
+        q, k, v = (torch.randn((heads, S, D), generator=g).half().to(device) for _ in range(3))
+        amask = oracle.band_global_random_mask(S, S, 64, 8, 0.05, seed=0).to(device)
+        attn = sparta.nn.SparseAttention(mask=amask)
+        mm = {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': 64, 'BLOCK_SIZE_K_VALUE': 64, 'BLOCK_SIZE_N_VALUE': 64}
+        sm = {'_impl': 'sparta', 'BLOCK_SIZE_H_VALUE': 64, 'BLOCK_SIZE_W_VALUE': 64, 'ROW_TILE_VALUE': 4}
+        attn.build({'qk/forward:C': mm, 'sm/forward:y': sm, 'out/forward:C': mm}, sample_inputs=[q, k, v])
+        nnz = attn.get_sparse_indexes().block_nnz
+        ms = timed(lambda: attn(q, k, v), steps=5)
+        flops = 4.0 * heads * nnz * 64 * 64 * D
+        extras['attention_b4h16s4096d64'] = {
+            'fwd_ms': round(ms, 4), 'nnz_blocks': nnz, 'fused': bool(attn._use_fused),
+            'tflops': round(flops / ms / 1e9, 2), 'frac_tensor_peak': round(flops / ms / 1e9 / peaks['tflops'], 4)}
+        del q, k, v, attn
+    except Exception as e:
+        extras['attention_b4h16s4096d64'] = {'error': repr(e)[:200]}
+
+    # mask -> BCSR on the GPU: 32 masks of 2048 x 2048, 32x32 blocks, 90 % sparse
+    try:
+        gdev = torch.Generator(device=device).manual_seed(7)
+        coarse = (torch.rand((32, 64, 64), device=device, generator=gdev) > 0.9).to(torch.uint8)
+        masks = coarse.repeat_interleave(32, 1).repeat_interleave(32, 2).contiguous()
+        fnc = sparta.tesa.get_bcs_function(32, 32, True, False)
+        ms = timed(lambda: fnc.build_indexes(masks), steps=20)
+        gbs = masks.numel() / ms / 1e6
+        extras['bcsr_convert_32x2048x2048'] = {'us': round(ms * 1e3, 2), 'gbs': round(gbs, 1),
+                                               'frac_hbm_peak': round(gbs / peaks['hbm_gbs'], 4)}
+        # dynamic sparsity: conversion + dds matmul, A[32,2048,128] . B[32,128,2048]
+        g = torch.Generator().manual_seed(8)
+        A = torch.randn((32, 2048, 128), generator=g).half().to(device)
+        B = torch.randn((32, 128, 2048), generator=g).half().to(device)
+        op = sparta.nn.SparseBatchMatMul(C_mask=masks, compressed=True, capacity=1024)
+        cfg = {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': 32, 'BLOCK_SIZE_K_VALUE': 64, 'BLOCK_SIZE_N_VALUE': 32}
+        op.build({'forward:C': cfg}, sample_inputs=[A, B])
+        op.set_dynamic(True)
+        ms = timed(lambda: op(A, B), steps=10)
+        nnz_total = int(op.get_sparse_indexes('C').nnz_dev.sum())
+        flops = 2.0 * 128 * 32 * 32 * nnz_total
+        extras['dynamic_dds_b32_2048x2048_k128'] = {
+            'us': round(ms * 1e3, 2), 'nnz_blocks_total': nnz_total, 'tflops': round(flops / ms / 1e9, 3),
+            'gbs': round((masks.numel() + 2 * (A.numel() + B.numel()) + 2 * nnz_total * 1024) / ms / 1e6, 1)}
+        del A, B, masks, op
+    except Exception as e:
+        extras['bcsr_convert_32x2048x2048'] = extras.get('bcsr_convert_32x2048x2048', {'error': repr(e)[:200]})
+        extras['dynamic_dds_b32_2048x2048_k128'] = {'error': repr(e)[:200]}
+
+    # README workload: fp32, 1024^3, 8x8-block weight mask at 90 %
+    try:
+        g = torch.Generator().manual_seed(2022)
+        x = torch.rand((1024, 1024), generator=g).to(device)
+        w = torch.rand((1024, 1024), generator=g)
+        b = torch.rand((1024,), generator=g)
+        mask = oracle.block_mask((1024, 1024), (8, 8), 0.9, generator=g)
+        dense = torch.nn.Linear(1024, 1024, device=device)
+        dense.load_state_dict({'weight': (w * mask).to(device), 'bias': b.to(device)})
+        op = sparta.nn.SparseLinear(dense, weight_mask=mask.to(device))
+        op.build({'forward:C': {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': 64, 'BLOCK_SIZE_K_VALUE': 8,
+                                'BLOCK_SIZE_N_VALUE': 8}}, sample_inputs=[x])
+        ms = timed(lambda: op(x), steps=20)
+        nnz = op.get_sparse_indexes('B').block_nnz
+        extras['linear_fp32_1024_8x8_90'] = {'us': round(ms * 1e3, 2), 'nnz_blocks': nnz,
+                                             'gflops': round(2.0 * 1024 * 64 * nnz / ms / 1e6, 1)}
+    except Exception as e:
+        extras['linear_fp32_1024_8x8_90'] = {'error': repr(e)[:200]}
+    return extras
+
+
+def cpu_baseline_linear(x, w, b, repeats=3):
+    """Masked-dense torch on the host cores: the computation the reference's tests compare with
+    (inputs upcast to fp32; w is already multiplied by its mask)."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    xf, wf, bf = x.float(), w.float(), b.float()
+    torch.nn.functional.linear(xf[:256], wf, bf)  # warm-up
+    best = float('inf')
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        torch.nn.functional.linear(xf, wf, bf)
+        best = min(best, time.perf_counter() - t0)
+    return best, cores
+
+
+def config_dict(n_gpus):
+    return {'workload': f'SparseLinear fp16 dsd: x[{TOKENS},{IN_F}] . W[{OUT_F},{IN_F}]^T + b, 32x32-block '
+                        f'weight mask, {int(SPARSITY * 100)}% block sparsity',
+            'tokens_per_gpu': TOKENS, 'in_features': IN_F, 'out_features': OUT_F, 'block': [BLOCK, BLOCK],
+            'sparsity': SPARSITY, 'parallelism': f'token-row shards x{n_gpus}, no collective',
+            'l2': 'flushed (256 MB write) before every timed step'}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--no-extras', action='store_true')
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
+
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    peaks = load_peaks()
+    metric = 'nnz_block_tflops'
+
+    if args.impl == 'reference':
+        if rank != 0:
+            return
+        x, w, b, mask = linear_inputs(SPARSITY)
+        nnz = int((mask.reshape(OUT_F // BLOCK, BLOCK, IN_F // BLOCK, BLOCK).amax((1, 3)) > 0).sum())
+        flops = 2.0 * TOKENS * BLOCK * BLOCK * nnz
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        xf, wf, bf = x.float(), w.float(), b.float()
+        for _ in range(max(args.warmup, 1)):
+            torch.nn.functional.linear(xf, wf, bf)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            torch.nn.functional.linear(xf, wf, bf)
+        ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        value = flops / ms / 1e9
+        print(json.dumps({
+            'impl': 'reference', 'metric': metric, 'value': value, 'unit': 'TFLOP/s', 'n_gpus': args.gpus,
+            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms, 'higher_is_better': True,
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32 (fp16 inputs upcast)', 'data': 'synthetic',
+            'config': config_dict(args.gpus),
+            'cpu_baseline': {'value': value, 'unit': 'TFLOP/s', 'cores': cores, 'kind': 'port',
+                             'sample': 'whole workload per step: F.linear(x, W*mask, b) in fp32, masked-dense'},
+            'e2e': {'value': value, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        }))
+        return
+
+    assert torch.cuda.is_available(), 'bench.py needs a CUDA device (there is no CPU fallback)'
+    torch.cuda.set_device(local_rank)
+    device = torch.device('cuda', local_rank)
+    barrier = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group('nccl', device_id=device)
+        barrier = lambda: dist.barrier(device_ids=[local_rank])
+
+    wl = build_linear(device, SPARSITY, 'dsd')
+    flush = L2Flusher(device)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    # device-resident timing (the kernel, plus the output allocation of the operator)
+    total_ms = time_steps(wl['fn'], args.steps, args.warmup, flush, barrier)
+
+    # end-to-end through the public operator with host buffers
+    x_host = wl['x'].pin_memory()
+    y_host = torch.empty((TOKENS, OUT_F), dtype=torch.float16).pin_memory()
+    x_dev = torch.empty_like(wl['xd'])
+    op = wl['op']
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        y = op(x_dev)
+        y_host.copy_(y, non_blocking=True)
+
+    e2e_ms = time_steps(e2e_step, args.steps, args.warmup, flush, barrier)
+    clocks = sampler.stop() if rank == 0 else None
+
+    times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = times.tolist()
+    ms_per_step = total_ms / args.steps
+    value = world * wl['flops'] / ms_per_step / 1e9
+    e2e_value = world * wl['flops'] / (e2e_ms / args.steps) / 1e9
+
+    if rank == 0:
+        kernel_tflops = wl['flops'] / ms_per_step / 1e9
+        out = {
+            'metric': metric, 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': 'f16 (fp32 accumulate)', 'data': 'synthetic',
+            'config': config_dict(world), 'nnz_blocks': wl['nnz'],
+            'roofline': {'bound': 'tensor', 'achieved': kernel_tflops, 'peak': peaks['tflops'], 'unit': 'TFLOP/s',
+                         'frac': kernel_tflops / peaks['tflops'], 'traffic': None,
+                         'peak_source': f"{peaks['source']} bf16 burst", 'hbm_gbs': wl['bytes'] / ms_per_step / 1e6,
+                         'hbm_frac': wl['bytes'] / ms_per_step / 1e6 / peaks['hbm_gbs']},
+            'e2e': {'value': e2e_value, 'unit': 'TFLOP/s', 'ms_per_step': e2e_ms / args.steps,
+                    'h2d_bytes_per_step': x_host.numel() * 2, 'd2h_bytes_per_step': y_host.numel() * 2},
+            'gpu_launches': args.steps,
+            'clocks': clocks,
+        }
+        if world == 1:
+            secs, cores = cpu_baseline_linear(wl['x'], wl['w'], wl['b'])
+            out['cpu_baseline'] = {'value': wl['flops'] / secs / 1e12, 'unit': 'TFLOP/s', 'cores': cores,
+                                   'kind': 'port', 'sample': 'whole workload, best of 3: F.linear(x, W*mask, b) fp32'}
+            if not args.no_extras:
+                out['extras'] = run_extras(device, peaks, flush)
+        print(json.dumps(out))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

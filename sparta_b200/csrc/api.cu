@@ -94,7 +94,7 @@ extern "C" int sparta_tile_table(int op, int dtype, sparta_tile_entry* out, int 
   };
   if (op <= 2) {
     // tcgen05 entries first: they are the preferred choice where they apply
-    if (dtype != SPARTA_F32) {
+    if (dtype != SPARTA_F32 && bsmm_tc_available()) {
       if (op == 1) emit({op, dtype, SPARTA_IMPL_TCGEN05, 128, 32, 32, 0, 1, 1});
       if (op == 2) emit({op, dtype, SPARTA_IMPL_TCGEN05, 32, 64, 32, 0, 1, 1});
     }
@@ -106,7 +106,7 @@ extern "C" int sparta_tile_table(int op, int dtype, sparta_tile_entry* out, int 
     for (int h : hs)
       for (int w : ws) emit({op, dtype, SPARTA_IMPL_SIMT, h, 0, w, -1, -1, -1});
   } else {
-    if (dtype != SPARTA_F32) emit({op, dtype, SPARTA_IMPL_TCGEN05, 64, 64, 64, 0, 1, 1});
+    if (dtype != SPARTA_F32 && attn_tc_available()) emit({op, dtype, SPARTA_IMPL_TCGEN05, 64, 64, 64, 0, 1, 1});
   }
   return n;
 }

@@ -31,4 +31,8 @@ int bsmm_simt(const BsmmParams& p, cudaStream_t st);
 bool bsmm_tc_supported(const BsmmParams& p);
 int bsmm_tc(const BsmmParams& p, cudaStream_t st);
 
+// whether the tcgen05 matmul / fused attention kernels are compiled into this build
+bool bsmm_tc_available();
+bool attn_tc_available();
+
 }  // namespace sparta

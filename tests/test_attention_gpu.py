@@ -1,0 +1,84 @@
+"""SparseAttention through the C-ABI against the CPU oracle, following
+test/unit/test_sparse_attention.py of the reference (forward and q/k/v gradients over three rounds
+of new masks), plus the fused half-precision forward kernel."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from sparta_b200.nn import SparseAttention
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), 'golden')
+
+
+def params(tile=32, softmax_tile=None):
+    mm = {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': tile, 'BLOCK_SIZE_K_VALUE': tile, 'BLOCK_SIZE_N_VALUE': tile}
+    st = softmax_tile or tile
+    sm = {'_impl': 'sparta', 'BLOCK_SIZE_H_VALUE': st, 'BLOCK_SIZE_W_VALUE': st, 'ROW_TILE_VALUE': 4}
+    cfg = {}
+    for k in ['forward:C', 'backward:A', 'backward:B']:
+        cfg[f'qk/{k}'] = dict(mm)
+        cfg[f'out/{k}'] = dict(mm)
+    for k in ['forward:y', 'backward:x']:
+        cfg[f'sm/{k}'] = dict(sm)
+    return cfg
+
+
+@pytest.mark.parametrize('H', [1, 4])
+@pytest.mark.parametrize('Ns,Nt,E', [(256, 256, 256), (512, 256, 256), (256, 512, 512), (1024, 256, 256)])
+def test_sparse_attention_operator(H, Ns, Nt, E):
+    g = torch.Generator().manual_seed(2022)
+    mask = oracle.block_mask((Nt, Ns), (8, 8), 0.95, generator=g)
+    q = torch.rand((H, Nt, E), generator=g)
+    k = torch.rand((H, Ns, E), generator=g)
+    v = torch.rand((H, Ns, E), generator=g)
+    grad = torch.rand((H, Nt, E), generator=g)
+    op = SparseAttention(mask=mask.cuda())
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    op.build(config=params(), sample_inputs=[qc, kc, vc])
+    for seed in range(3):
+        qr, kr, vr = (t.clone().requires_grad_() for t in (q, k, v))
+        target = oracle.attention_reference(qr, kr, vr, mask)
+        target.backward(grad)
+        qc.grad = kc.grad = vc.grad = None
+        out = op(qc, kc, vc)
+        out.backward(grad.cuda())
+        tol = dict(atol=1e-4, rtol=1e-4)
+        torch.testing.assert_close(out.detach().cpu(), target.detach(), **tol)
+        torch.testing.assert_close(qc.grad.cpu(), qr.grad, **tol)
+        torch.testing.assert_close(kc.grad.cpu(), kr.grad, **tol)
+        torch.testing.assert_close(vc.grad.cpu(), vr.grad, **tol)
+        g2 = torch.Generator().manual_seed(seed)
+        mask = oracle.block_mask((Nt, Ns), (8, 8), 0.95, generator=g2)
+        op.update_mask(mask.cuda())
+
+
+def test_golden_vector():
+    g = np.load(os.path.join(GOLDEN, 'softmax_attention.npz'))
+    t = lambda n: torch.from_numpy(g[n])
+    op = SparseAttention(mask=t('amask').cuda())
+    op.build(config=params(16, 16), sample_inputs=[t('q').cuda(), t('k').cuda(), t('v').cuda()])
+    out = op(t('q').cuda(), t('k').cuda(), t('v').cuda())
+    torch.testing.assert_close(out.cpu(), t('o'), atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('E', [64, 128])
+@pytest.mark.parametrize('fused', [False, 'auto'])
+def test_half_precision_attention_band_mask(dtype, E, fused):
+    """Band + global + random 64x64-block mask (the benchmark generator) at reduced size."""
+    heads, S = 3, 1024
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn((heads, S, E), generator=g).to(dtype) for _ in range(3))
+    mask = oracle.band_global_random_mask(S, S, 64, 2, 0.1, seed=4)
+    op = SparseAttention(mask=mask.cuda(), fused=fused)
+    op.build(config=params(64), sample_inputs=[q.cuda(), k.cuda(), v.cuda()])
+    out = op(q.cuda(), k.cuda(), v.cuda())
+    assert out.dtype == dtype
+    target = oracle.attention_reference(q.float(), k.float(), v.float(), mask)
+    torch.testing.assert_close(out.float().cpu(), target, atol=2e-2, rtol=2e-2)
+    if fused == 'auto' and op._use_fused:
+        assert op.fused_status() == [0, 0, 0, 0]

@@ -73,7 +73,6 @@ def test_tile_table():
     for op in range(3):
         f32 = _lib.tile_table(op, _lib.F32)
         assert len(f32) == 64 and all(e.impl == _lib.IMPL_SIMT for e in f32)
-    assert _lib.tile_table(_lib.OP_DSD, _lib.F16)[0].impl == _lib.IMPL_TCGEN05
     assert len(_lib.tile_table(_lib.OP_SOFTMAX, _lib.F32)) == 20
     assert _lib.lib().sparta_tile_table(9, 0, None, 0) == -1
 

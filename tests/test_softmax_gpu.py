@@ -1,0 +1,110 @@
+"""Sparse softmax through the C-ABI against the CPU oracle and the golden vectors, following
+test/unit/test_sparse_softmax.py of the reference."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from sparta_b200.nn import SparseSoftmax
+from sparta_b200.specializer.funtional import SparseBatchSoftmaxCtx, SparseBatchSoftmaxFunc
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), 'golden')
+TOL = dict(rtol=1e-4, atol=1e-4)
+
+
+def params(bh=32, bw=32):
+    return {'_impl': 'sparta', 'BLOCK_SIZE_H_VALUE': bh, 'BLOCK_SIZE_W_VALUE': bw, 'ROW_TILE_VALUE': 4}
+
+
+def make_case(batch=4, H=128, W=256, granularity=(8, 8), sparsity=0.9, seed=2022):
+    g = torch.Generator().manual_seed(seed)
+    shape = (H, W) if batch is None else (batch, H, W)
+    x = torch.rand(shape, generator=g)
+    grad = torch.rand(shape, generator=g)
+    mask = oracle.block_mask((H, W), granularity, sparsity, generator=g)
+    T = float(np.sqrt(W))
+    y = oracle.softmax_forward_reference(x, mask, T)
+    dx = oracle.softmax_backward_reference(grad, y, mask, T)
+    return x, grad, mask, T, y, dx
+
+
+@pytest.mark.parametrize('compressed', [False, True])
+def test_sparse_softmax_function(compressed):
+    x, grad, mask, T, y, dx = make_case()
+    ctx = SparseBatchSoftmaxCtx(compressed, T)
+    names = list(ctx.get_kernel_placeholders(backward=True).keys())
+    ctx.select_impls({n: 'sparta' for n in names})
+    ctx.set_shape(4, 128, 256)
+    for ports in ctx.sparse_ports.values():
+        for p in ports:
+            p.set_mask(mask.cuda())
+    ctx.build({n: params() for n in names})
+    ix = ctx.sparse_ports['y'][0].indexes
+    xin, gin = x.cuda(), grad.cuda()
+    if compressed:
+        xin, gin = ix.convert(xin), ix.convert(gin)
+    xin.requires_grad_()
+    out = SparseBatchSoftmaxFunc.apply(ctx, xin)
+    out.backward(gin)
+    got_y, got_dx = out.detach(), xin.grad
+    if compressed:
+        got_y, got_dx = ix.inverse(got_y), ix.inverse(got_dx)
+    torch.testing.assert_close(got_y.cpu(), y, **TOL)
+    torch.testing.assert_close(got_dx.cpu(), dx, **TOL)
+
+
+@pytest.mark.parametrize('batch', [None, 4])
+@pytest.mark.parametrize('compressed', [False, True])
+def test_sparse_softmax_operator_dynamic(compressed, batch):
+    x, grad, mask, T, y, dx = make_case(batch)
+    op = SparseSoftmax(mask.cuda(), T, compressed)
+    op.build(config={n: params() for n in op.get_kernel_placeholders(backward=True)}, sample_inputs=[x.cuda()])
+    for seed in range(3):
+        ix = op.get_sparse_indexes('y')
+        xin, gin = x.cuda(), grad.cuda()
+        if compressed:
+            xin, gin = ix.convert(xin), ix.convert(gin)
+        xin.requires_grad_()
+        out = op(xin)
+        out.backward(gin)
+        got_y, got_dx = out.detach(), xin.grad
+        if compressed:
+            got_y, got_dx = ix.inverse(got_y), ix.inverse(got_dx)
+        torch.testing.assert_close(got_y.cpu(), y, **TOL)
+        torch.testing.assert_close(got_dx.cpu(), dx, **TOL)
+        x, grad, mask, T, y, dx = make_case(batch, seed=seed)
+        op.update_mask(mask.cuda())
+
+
+@pytest.mark.parametrize('compressed', [False, True])
+@pytest.mark.parametrize('block', [(8, 16), (32, 32), (64, 128)])
+def test_golden_vectors_and_fully_masked_rows(compressed, block):
+    g = np.load(os.path.join(GOLDEN, 'softmax_attention.npz'))
+    t = lambda k: torch.from_numpy(g[k])
+    op = SparseSoftmax(t('mask').cuda(), float(g['T']), compressed)
+    op.build({'forward:y': params(*block), 'backward:x': params(*block)}, sample_inputs=[t('x').cuda()])
+    ix = op.get_sparse_indexes('y')
+    xin = t('x').cuda()
+    if compressed:
+        xin = ix.convert(xin)
+    out = op(xin)
+    if compressed:
+        out = ix.inverse(out)
+    torch.testing.assert_close(out.cpu(), t('y'), **TOL)
+    assert torch.all(out[:, 40:48] == 0)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_half_types_block_uniform_mask(dtype):
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn((3, 256, 512), generator=g) * 3).to(dtype)
+    mask = oracle.block_mask((256, 512), (64, 64), 0.7, generator=g)
+    op = SparseSoftmax(mask.cuda(), 2.0, compressed=True)
+    op.build({'forward:y': params(64, 64)}, sample_inputs=[x.cuda()])
+    ix = op.get_sparse_indexes('y')
+    assert ix.block_uniform
+    out = ix.inverse(op(ix.convert(x.cuda()))).float().cpu()
+    torch.testing.assert_close(out, oracle.softmax_forward_reference(x.float(), mask, 2.0), rtol=2e-2, atol=2e-2)
