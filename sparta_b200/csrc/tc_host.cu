@@ -1,0 +1,71 @@
+// Host-side support of the tcgen05 kernels: tensor-map encoding and the device status words.
+#include <mutex>
+
+#include "tc_common.cuh"
+
+namespace sparta {
+namespace tc {
+
+__device__ int32_t g_status[4];
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int make_tensor_map(CUtensorMap* map, const void* base, int dtype, int rank, const uint64_t* dims,
+                    const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return SPARTA_ERR_DRIVER;
+  if (!aligned(base, 16)) return SPARTA_ERR_ALIGN;
+  CUtensorMapDataType dt;
+  if (dtype == SPARTA_F16) dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  else if (dtype == SPARTA_BF16) dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  else return SPARTA_ERR_UNSUPPORTED;
+  cuuint64_t d[5], s[4];
+  cuuint32_t b[5], e[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    e[i] = 1;
+    if (i + 1 < rank) {
+      s[i] = strides_bytes[i];
+      if (s[i] % 16) return SPARTA_ERR_ALIGN;
+    }
+  }
+  CUresult r = fn(map, dt, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? SPARTA_OK : SPARTA_ERR_DRIVER;
+}
+
+int32_t* device_status_ptr() {
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_status) != cudaSuccess) return nullptr;
+  return static_cast<int32_t*>(p);
+}
+
+int read_and_clear_status(int32_t out[4]) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int32_t) * 4);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const int32_t zero[4] = {0, 0, 0, 0};
+  e = cudaMemcpyToSymbol(g_status, zero, sizeof(zero));
+  return e == cudaSuccess ? SPARTA_OK : static_cast<int>(e);
+}
+
+}  // namespace tc
+}  // namespace sparta
+
+// Reads (and clears) the status words of the current device: all zero unless a kernel's bounded wait
+// ran out.  Synchronises the device.  No counterpart in the reference, whose kernels have no waits.
+extern "C" int sparta_last_status(int32_t h_out[4]) {
+  if (!h_out) return SPARTA_ERR_BAD_ARG;
+  return sparta::tc::read_and_clear_status(h_out);
+}

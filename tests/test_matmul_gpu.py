@@ -119,7 +119,10 @@ def reference_grads(data, mask, mode, trans_A, trans_B, biased, block):
     A = data['A'].clone().requires_grad_()
     B = data['B'].clone().requires_grad_()
     bias = data['bias'].clone().requires_grad_() if biased else None
-    C = oracle.matmul_reference(A, B, bias, mask, mode, trans_A, trans_B, block)
+    # data['A'] / data['B'] are already multiplied by the element mask; differentiate with respect to
+    # that masked tensor, so its gradient is the dense gradient restricted to the covered blocks
+    ones = torch.ones_like(mask)
+    C = oracle.matmul_reference(A, B, bias, mask if mode == 'dds' else ones, mode, trans_A, trans_B, block)
     cover = torch.from_numpy(oracle.block_cover_mask(mask.numpy(), *block)).float()
     grad_C = data['grad_C'] * cover if mode == 'dds' else data['grad_C']
     C.backward(grad_C)
