@@ -213,6 +213,12 @@ typedef struct sparta_tile_entry {
 
 int sparta_tile_table(int op, int dtype, sparta_tile_entry* out_entries, int max_entries);
 
+/* Status words of the tcgen05 kernels on the current device: all zero unless a bounded wait (on an
+ * mbarrier) ran out, in which case the kernel stopped early and its output is invalid.  Word 0:
+ * producer, 1: MMA issuer, 2: epilogue, 3: reserved.  Synchronises the device and clears the words.
+ * No counterpart in the reference, whose kernels contain no waits. */
+int sparta_last_status(int32_t h_out[4]);
+
 /* Whether the running device can execute this library's kernels (compute capability 10.x). */
 int sparta_device_supported(int device);
 

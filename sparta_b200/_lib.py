@@ -70,6 +70,7 @@ SIGNATURES = {
     'sparta_attn_fwd': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                 c_void_p, c_void_p, c_size_t, c_void_p]),
+    'sparta_last_status': (c_int, [POINTER(c_int32)]),
     'sparta_tile_table': (c_int, [c_int, c_int, POINTER(TileEntry), c_int]),
 }
 
@@ -132,3 +133,10 @@ def tile_table(op: int, dtype: int = F32):
     buf = (TileEntry * max(n, 1))()
     lib().sparta_tile_table(op, dtype, buf, n)
     return [buf[i] for i in range(n)]
+
+
+def last_status():
+    """Status words of the tcgen05 kernels (synchronises the device); all zero when clean."""
+    buf = (c_int32 * 4)()
+    check(lib().sparta_last_status(buf), 'sparta_last_status')
+    return list(buf)

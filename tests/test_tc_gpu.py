@@ -1,0 +1,68 @@
+"""The tcgen05 / TMEM / TMA kernels through the C-ABI against the CPU oracle (2e-2 for fp16 / bf16),
+forced with ``_family='tcgen05'`` so that a silent fall-back to the FMA kernel cannot pass."""
+import pytest
+import torch
+
+from oracle import oracle
+from sparta_b200 import _lib
+from sparta_b200.specializer.kernels import SparTASparseMatMulKernel
+
+pytestmark = pytest.mark.gpu
+TOL = dict(rtol=2e-2, atol=2e-2)
+
+
+def _dsd_case(batch, M, K, N, sparsity, dtype, biased, seed, empty_rows=()):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((batch, M, K), generator=g).to(dtype)
+    w = (torch.randn((batch, N, K), generator=g) * 0.1).to(dtype)
+    b = torch.randn((batch, N), generator=g).to(dtype) if biased else None
+    mask = oracle.block_mask((N, K), (32, 32), sparsity, generator=g)
+    for r in empty_rows:
+        mask[r * 32:(r + 1) * 32] = 0
+    return x, w * mask, b, mask
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('biased', [False, True])
+@pytest.mark.parametrize('batch,M,K,N,sparsity', [
+    (1, 128, 64, 32, 0.0),      # one tile, two K blocks
+    (2, 256, 256, 192, 0.5),    # partial panel (6 block columns), batch
+    (1, 512, 1024, 1024, 0.9),  # several panels, sparse rows
+    (1, 384, 2048, 544, 0.75),  # 17 block columns: a full and a one-column panel
+])
+def test_dsd_tcgen05(dtype, biased, batch, M, K, N, sparsity):
+    x, w, b, mask = _dsd_case(batch, M, K, N, sparsity, dtype, biased, seed=M + K + N,
+                              empty_rows=(1,) if N >= 192 else ())
+    kernel = SparTASparseMatMulKernel(mode='dsd', biased=biased, transpose_A=False, transpose_B=True,
+                                      compressed=True)
+    kernel.ports['B'].set_mask(mask.cuda())
+    kernel.set_shape(batch, M, K, N)
+    kernel.compile({'_impl': 'sparta', '_family': 'tcgen05', 'BLOCK_SIZE_M_VALUE': 128,
+                    'BLOCK_SIZE_K_VALUE': 32, 'BLOCK_SIZE_N_VALUE': 32})
+    ix = kernel.ports['B'].indexes
+    args = [x.cuda(), ix.convert(w.cuda())] + ([b.cuda()] if biased else [])
+    out = kernel(*args)
+    assert _lib.last_status() == [0, 0, 0, 0]
+    expect = oracle.matmul_reference(x.float(), w.float(), b.float() if biased else None, mask, 'dsd',
+                                     False, True, (32, 32))
+    torch.testing.assert_close(out.float().cpu(), expect, **TOL)
+    # same answer as the FMA kernel on the same inputs (tighter: both accumulate in fp32)
+    kernel.compile({'_impl': 'sparta', '_family': 'simt', 'BLOCK_SIZE_M_VALUE': 64,
+                    'BLOCK_SIZE_K_VALUE': 32, 'BLOCK_SIZE_N_VALUE': 32})
+    ref = kernel(*args)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+def test_dsd_tcgen05_is_deterministic():
+    x, w, b, mask = _dsd_case(1, 256, 512, 512, 0.8, torch.float16, True, seed=3)
+    kernel = SparTASparseMatMulKernel(mode='dsd', biased=True, transpose_A=False, transpose_B=True,
+                                      compressed=True)
+    kernel.ports['B'].set_mask(mask.cuda())
+    kernel.set_shape(1, 256, 512, 512)
+    kernel.compile({'_impl': 'sparta', '_family': 'tcgen05', 'BLOCK_SIZE_M_VALUE': 128,
+                    'BLOCK_SIZE_K_VALUE': 32, 'BLOCK_SIZE_N_VALUE': 32})
+    ix = kernel.ports['B'].indexes
+    args = [x.cuda(), ix.convert(w.cuda()), b.cuda()]
+    a = kernel(*args)
+    c = kernel(*args)
+    assert torch.equal(a, c)
