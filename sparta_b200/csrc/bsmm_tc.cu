@@ -3,17 +3,26 @@
 // dsd, B stored [N, K] as BCSR 32 x 32 blocks (the SparseLinear weight layout):
 //   C[m, n] = sum over kept K-blocks k of row-block n:  X[m, k-block] . W_block(n, k)^T   (+ bias)
 //
-// One CTA owns 128 token rows x a panel of NP block columns (NP * 32 output features), i.e. NP fp32
-// accumulators of 128 x 32 in tensor memory.  It walks the K-blocks that ANY row-block of the panel
-// keeps, in ascending order (an NP-way merge of the sorted BCSR rows done by the producer warp), so
-// each 128 x 32 tile of X is staged once per panel and shared by every W block of that K-block.
-//   warp 4    producer: merge + TMA loads (X tile by coordinate, W blocks gathered by BCSR position)
-//   warp 5    one thread issues tcgen05.mma (M128 N32 K16, two per W block) and commits
+// One CTA owns 128 token rows x a panel of NP = 8 block columns (256 output features), i.e. NP fp32
+// accumulators of 128 x 32 in tensor memory.  Its prologue turns the BCSR rows of the panel into a
+// schedule in shared memory: kmask[k] = which row-blocks of the panel keep K-block k.  Producer and
+// MMA warps then walk k = 0 .. K/32 over that schedule independently (no per-step messages, no
+// shuffles), so each 128 x 32 tile of X is staged once per panel and shared by every W block of
+// that K-block.
+//   warp 4    producer: TMA loads (X tile by coordinate, W blocks gathered by BCSR position) into two
+//             rings -- X tiles and W blocks -- each load completing on the step's mbarrier
+//   warps 5-8 MMA issue: each warp owns a quarter of the accumulators and one of its threads issues
+//             tcgen05.mma (M128 N32 K16, two per W block); its tcgen05.commit arrives on the step's
+//             "empty" mbarrier, which frees the ring slots once all four have arrived.  Several
+//             issuers are used because one thread sustains only about one such small MMA per 120
+//             cycles, while the tensor pipe takes one per ~64 cycles (measured with ncu).
 //   warps 0-3 epilogue: tcgen05.ld -> + bias -> fp16 / bf16 -> global
+// Two CTAs are resident per SM (256 TMEM columns, ~98 KB of shared memory each), so the prologue and
+// epilogue of one overlap the main loop of the other.
 // Every mbarrier wait is bounded; a wait that runs out sets a status word and the CTA winds down.
 //
 // Replaces sparta_sparse_matmul_dsd.cuh.j2 / openai_sparse_matmul_dsd.cuh.j2 for this layout.
-#include <cstdlib>
+#include <type_traits>
 
 #include "bsmm.cuh"
 #include "tc_common.cuh"
@@ -25,11 +34,12 @@ using namespace tc;
 
 constexpr int kBlk = 32;            // BCSR block edge (K and N)
 constexpr int kTileM = 128;         // token rows per CTA
-constexpr int kStages = 4;
 constexpr int kXBytes = kTileM * kBlk * 2;   // 8 KB: 128 rows x 64 B
 constexpr int kWBytes = kBlk * kBlk * 2;     // 2 KB
-constexpr int kMaxRowBlocks = 512;  // K-blocks per W row-block held in shared memory
-constexpr int kThreads = 192;
+constexpr int kPanel = 8;           // block columns per CTA: 256 TMEM columns, two CTAs resident per SM
+constexpr int kMaxKb = 1024;        // K-blocks the schedule can hold (K <= 32768)
+constexpr int kMmaWarps = 4;        // MMA-issuing warps; each owns the accumulators l with l % kMmaWarps == its index
+constexpr int kThreads = 160 + 32 * kMmaWarps;
 
 struct DsdTcParams {
   const int32_t* row_ptr;
@@ -41,170 +51,183 @@ struct DsdTcParams {
   int32_t* status;
 };
 
+// Shared-memory rings.  A "step" is one K-block of the schedule: one X tile (ring of kSteps slots)
+// plus one W block per row-block of the panel that keeps this K-block (ring of kWSlots slots, taken
+// in order).  Decoupling the two rings keeps the loads in flight independent of the mask density.
 template <int NP>
 struct SmemLayout {
-  static constexpr int kStageBytes = kXBytes + NP * kWBytes;
-  static constexpr int kIdxBytes = NP * kMaxRowBlocks * 2;
-  static constexpr int kTotal = kStages * kStageBytes + kIdxBytes + 1024 /* barriers etc. */ + 1024 /* align */;
+  static constexpr int kSteps = NP == 16 ? 12 : 6;    // steps (X tiles) in flight
+  static constexpr int kWSlots = NP == 16 ? 44 : 22;  // W blocks in flight
+  static constexpr int kXRing = kSteps * kXBytes;
+  static constexpr int kWRing = kWSlots * kWBytes;
+  static constexpr int kMaskBytes = kMaxKb * 4;
+  static constexpr int kBiasBytes = NP * kBlk * 4;
+  static constexpr int kCtlBytes = 512;
+  static constexpr int kTotal = kXRing + kWRing + kMaskBytes + kBiasBytes + kCtlBytes + 1024 /* align */;
 };
 
 template <int NP, int FMT>
 __global__ void __launch_bounds__(kThreads, 1)
 bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    DsdTcParams p) {
+  using T = typename std::conditional<FMT == 0, __half, __nv_bfloat16>::type;
+  using L = SmemLayout<NP>;
+  constexpr int kSteps = L::kSteps, kWSlots = L::kWSlots;
+  constexpr uint32_t kTmemCols = NP * kBlk;
+  constexpr int kIssuers = kMmaWarps;
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  using L = SmemLayout<NP>;
-  uint8_t* stage_base = smem;
-  uint16_t* s_idx = reinterpret_cast<uint16_t*>(smem + kStages * L::kStageBytes);
-  uint8_t* ctl = smem + kStages * L::kStageBytes + L::kIdxBytes;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctl);            // [kStages]
-  uint64_t* empty_bar = full_bar + kStages;                         // [kStages]
-  uint64_t* accum_bar = empty_bar + kStages;                        // [1]
-  uint32_t* stage_mask = reinterpret_cast<uint32_t*>(accum_bar + 1);  // [kStages]
-  uint32_t* tmem_holder = stage_mask + kStages;
-  uint32_t* s_written = tmem_holder + 1;
-  int* s_row_len = reinterpret_cast<int*>(s_written + 1);           // [NP]
-  int* s_row_start = s_row_len + NP;                                // [NP]
+  uint8_t* x_ring = smem;
+  uint8_t* w_ring = smem + L::kXRing;
+  uint32_t* kmask = reinterpret_cast<uint32_t*>(smem + L::kXRing + L::kWRing);
+  float* s_bias = reinterpret_cast<float*>(smem + L::kXRing + L::kWRing + L::kMaskBytes);
+  uint8_t* ctl = smem + L::kXRing + L::kWRing + L::kMaskBytes + L::kBiasBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctl);   // [kSteps] loads of a step have landed
+  uint64_t* empty_bar = full_bar + kSteps;                 // [kSteps] MMAs of a step have read smem
+  uint64_t* accum_bar = empty_bar + kSteps;                // [1]     all MMAs of the tile are done
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  int* s_range = reinterpret_cast<int*>(tmem_holder + 1);  // [2] BCSR entries of the panel
+  int* s_row_start = s_range + 2;                          // [NP]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int panel = blockIdx.x, m0 = blockIdx.y * kTileM, batch = blockIdx.z;
-  constexpr uint32_t kTmemCols = NP * kBlk;
+  const int nb0 = panel * NP;
+  const int nb_end = min(nb0 + NP, p.Nb);
 
+  // ------------------------------ prologue ------------------------------
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kSteps; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+      mbar_init(&empty_bar[s], kIssuers);
     }
-    mbar_init(accum_bar, 2);
+    mbar_init(accum_bar, kIssuers);
     fence_mbar_init();
-    *s_written = 0;
+    s_range[0] = p.row_ptr[nb0];
+    s_range[1] = p.row_ptr[nb_end];
   }
   if (warp == 4 && lane == 0) {
     prefetch_tensormap(&tm_x);
     prefetch_tensormap(&tm_w);
   }
   if (warp == 5) tmem_alloc<kTmemCols>(tmem_holder);
-  // stage the BCSR rows of this panel (column numbers only) in shared memory
-  if (threadIdx.x < NP) {
-    const int nb = panel * NP + threadIdx.x;
-    int start = 0, len = 0;
-    if (nb < p.Nb) {
-      start = p.row_ptr[nb];
-      len = p.row_ptr[nb + 1] - start;
+  if (threadIdx.x >= 64 && threadIdx.x < 64 + NP) {
+    const int l = threadIdx.x - 64;
+    s_row_start[l] = nb0 + l < p.Nb ? p.row_ptr[nb0 + l] : 0;
+  }
+  for (int k = threadIdx.x; k < p.Kb; k += kThreads) kmask[k] = 0;
+  {
+    const T* bias = p.bias ? static_cast<const T*>(p.bias) + (long long)batch * p.N : nullptr;
+    for (int j = threadIdx.x; j < NP * kBlk; j += kThreads) {
+      const int n = nb0 * kBlk + j;
+      s_bias[j] = (bias && n < p.N) ? to_float(bias[n]) : 0.f;
     }
-    s_row_start[threadIdx.x] = start;
-    s_row_len[threadIdx.x] = len;
   }
   __syncthreads();
-  for (int l = 0; l < NP; ++l) {
-    const int start = s_row_start[l], len = s_row_len[l];
-    for (int j = threadIdx.x; j < len; j += kThreads)
-      s_idx[l * kMaxRowBlocks + j] = static_cast<uint16_t>(p.idx[start + j] & 0xffff);
+  // the rows of a panel are consecutive in the BCSR array: entry = (row-block << 16) | K-block
+  for (int e = s_range[0] + threadIdx.x; e < s_range[1]; e += kThreads) {
+    const int v = __ldg(p.idx + e);
+    atomicOr(&kmask[v & 0xffff], 1u << ((v >> 16) - nb0));
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
+  uint32_t written = 0;  // which accumulators receive any product
 
   if (warp == 4) {
     // ------------------------------ producer ------------------------------
-    int cur = 0;
-    const int len = lane < NP ? s_row_len[lane] : 0;
-    const int vbase = lane < NP ? s_row_start[lane] : 0;
-    const uint16_t* my = s_idx + (lane < NP ? lane : 0) * kMaxRowBlocks;
-    int kcur = cur < len ? my[cur] : 0x7fffffff;
-    int stage = 0;
-    uint32_t phase = 0;
-    while (true) {
-      int kmin = kcur;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
-      const bool last = (kmin == 0x7fffffff);
-      const uint32_t active = __ballot_sync(0xffffffffu, !last && kcur == kmin);
-      int ok = 1;
-      if (lane == 0) ok = mbar_wait(&empty_bar[stage], phase ^ 1) ? 1 : 0;
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) {
-        if (lane == 0) atomicExch(&p.status[0], 1);
-        break;
+    // All lanes run the same bookkeeping; lane l also owns the cursor into BCSR row nb0 + l.
+    long long wrow = 0;  // row of this lane's next W block in the [blocks * 32, 32] view of the values
+    if (lane < NP) wrow = ((long long)batch * p.val_stride_blocks + s_row_start[lane]) * kBlk;
+    int slot = 0, tail = 0, inflight = 0, w_used = 0, w_head = 0;
+    uint32_t tail_phase = 0;
+    uint64_t cnts = 0;  // W blocks held by each in-flight step, 5 bits per ring slot
+    bool ok = true;
+    uint32_t m_next = p.Kb > 0 ? kmask[0] : 0;
+    for (int k = 0; k < p.Kb; ++k) {
+      const uint32_t m = m_next;
+      m_next = (k + 1 < p.Kb) ? kmask[k + 1] : 0;
+      if (!m) continue;
+      const int need = __popc(m);
+      while (inflight == kSteps || w_used + need > kWSlots) {  // free the oldest step
+        if (!mbar_wait(&empty_bar[tail], tail_phase)) { ok = false; break; }
+        w_used -= (int)((cnts >> (5 * tail)) & 31u);
+        --inflight;
+        if (++tail == kSteps) { tail = 0; tail_phase ^= 1; }
       }
-      uint8_t* st = stage_base + stage * L::kStageBytes;
-      if (last) {
-        if (lane == 0) {
-          stage_mask[stage] = 0x80000000u;
-          mbar_arrive(&full_bar[stage]);
-        }
-        break;
-      }
+      if (!ok) break;
       if (lane == 0) {
-        stage_mask[stage] = active;
-        mbar_arrive_expect_tx(&full_bar[stage], kXBytes + __popc(active) * kWBytes);
-        tma_load_2d(st, &tm_x, kmin * kBlk, batch * p.M + m0, &full_bar[stage]);
+        mbar_arrive_expect_tx(&full_bar[slot], kXBytes + need * kWBytes);
+        tma_load_2d(x_ring + slot * kXBytes, &tm_x, k * kBlk, batch * p.M + m0, &full_bar[slot]);
       }
-      __syncwarp();
-      if ((active >> lane) & 1u) {
-        const long long blk = (long long)batch * p.val_stride_blocks + vbase + cur;
-        tma_load_2d(st + kXBytes + lane * kWBytes, &tm_w, 0, (int)(blk * kBlk), &full_bar[stage]);
-        ++cur;
-        kcur = cur < len ? my[cur] : 0x7fffffff;
+      if ((m >> lane) & 1u) {
+        int ws = w_head + __popc(m & ((1u << lane) - 1u));  // rank among the kept row-blocks
+        if (ws >= kWSlots) ws -= kWSlots;
+        tma_load_2d(w_ring + ws * kWBytes, &tm_w, 0, (int)wrow, &full_bar[slot]);
+        wrow += kBlk;
       }
-      if (++stage == kStages) { stage = 0; phase ^= 1; }
+      cnts = (cnts & ~(31ull << (5 * slot))) | ((uint64_t)need << (5 * slot));
+      w_head += need;
+      if (w_head >= kWSlots) w_head -= kWSlots;
+      w_used += need;
+      ++inflight;
+      if (++slot == kSteps) slot = 0;
     }
-  } else if (warp == 5) {
+    if (!ok && lane == 0) atomicExch(&p.status[0], 1);
+  } else if (warp >= 5 && warp < 5 + kIssuers) {
     // ------------------------------ MMA issue ------------------------------
+    // Operand addresses derive from loop counters only, so they stay warp-uniform; one lane issues.
     constexpr uint32_t idesc = make_idesc_f16(kTileM, kBlk, FMT, 0, 0);
-    uint32_t written = 0;
-    int stage = 0;
-    uint32_t phase = 0;
-    while (true) {
-      if (!mbar_wait(&full_bar[stage], phase)) {
-        if (lane == 0) atomicExch(&p.status[1], 1);
-        break;
-      }
-      const uint32_t mask = stage_mask[stage];
-      if (mask & 0x80000000u) break;
+    const uint32_t x_base = smem_u32(x_ring), w_base = smem_u32(w_ring);
+    const uint64_t desc_hi = make_smem_desc(0, 16, 512, SW_64B);
+    const bool leader = lane == 0;
+    uint32_t mine = 0;  // accumulators issued by this warp
+    for (int l = warp - 5; l < NP; l += kIssuers) mine |= 1u << l;
+    int slot = 0;
+    uint32_t phase = 0, ws = 0;  // ws: next W slot, advances exactly like the producer's ring head
+    bool ok = true;
+    uint32_t m_next = p.Kb > 0 ? kmask[0] : 0;
+    for (int k = 0; k < p.Kb; ++k) {
+      const uint32_t mask = m_next;
+      m_next = (k + 1 < p.Kb) ? kmask[k + 1] : 0;
+      if (!mask) continue;
+      if (!mbar_wait(&full_bar[slot], phase)) { ok = false; break; }
       tc_fence_after_sync();
-      if (lane == 0) {
-        const uint32_t a_addr = smem_u32(stage_base + stage * L::kStageBytes);
-        uint32_t m = mask;
-        while (m) {
-          const int l = __ffs(m) - 1;
-          m &= m - 1;
-          const uint32_t b_addr = a_addr + kXBytes + l * kWBytes;
-          const uint32_t acc = (written >> l) & 1u;
-#pragma unroll
-          for (int kk = 0; kk < kBlk / 16; ++kk) {
-            const uint64_t a_desc = make_smem_desc(a_addr + kk * 32, 16, 512, SW_64B);
-            const uint64_t b_desc = make_smem_desc(b_addr + kk * 32, 16, 512, SW_64B);
-            umma_ss(tmem_base + l * kBlk, a_desc, b_desc, idesc, acc | (kk > 0 ? 1u : 0u));
-          }
+      const uint32_t a_lo = (x_base + slot * kXBytes) >> 4;
+      uint32_t m = mask & mine;
+      while (m) {
+        const int l = __ffs(m) - 1;
+        m &= m - 1;
+        uint32_t w = ws + __popc(mask & ((1u << l) - 1u));  // rank of block l among the step's blocks
+        if (w >= kWSlots) w -= kWSlots;
+        const uint32_t b_lo = (w_base + w * kWBytes) >> 4;
+        const uint32_t acc = (written >> l) & 1u;
+        if (leader) {
+          umma_ss(tmem_base + l * kBlk, desc_hi | a_lo, desc_hi | b_lo, idesc, acc);
+          umma_ss(tmem_base + l * kBlk, desc_hi | (a_lo + 2), desc_hi | (b_lo + 2), idesc, 1u);
         }
-        umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
       }
-      __syncwarp();
+      ws += __popc(mask);
+      if (ws >= kWSlots) ws -= kWSlots;
+      if (leader) umma_commit(&empty_bar[slot]);  // frees the step's X tile and W blocks when read
       written |= mask;
-      if (++stage == kStages) { stage = 0; phase ^= 1; }
+      if (++slot == kSteps) { slot = 0; phase ^= 1; }
     }
-    if (lane == 0) {
-      *s_written = written;
-      umma_commit(accum_bar);
-      mbar_arrive(accum_bar);
-    }
-  } else {
+    if (!ok && lane == 0) atomicExch(&p.status[1], 1);
+    if (leader) umma_commit(accum_bar);
+  } else if (warp < 4) {
     // ------------------------------ epilogue ------------------------------
-    using T = typename std::conditional<FMT == 0, __half, __nv_bfloat16>::type;
+    for (int k = lane; k < p.Kb; k += 32) written |= kmask[k];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) written |= __shfl_xor_sync(0xffffffffu, written, o);
     if (!mbar_wait(accum_bar, 0)) {
       if (lane == 0) atomicExch(&p.status[2], 1);
     } else {
       tc_fence_after_sync();
-      const uint32_t written = *s_written;
       const int row = m0 + warp * 32 + lane;
       T* crow = static_cast<T*>(p.C) + ((long long)batch * p.M + row) * p.N;
-      const T* bias = p.bias ? static_cast<const T*>(p.bias) + (long long)batch * p.N : nullptr;
-      for (int l = 0; l < NP; ++l) {
-        const int nb = panel * NP + l;
-        if (nb >= p.Nb) break;
+      for (int l = 0; l < nb_end - nb0; ++l) {
         uint32_t r[32];
         if ((written >> l) & 1u) {
           tmem_ld_x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + l * kBlk, r);
@@ -216,11 +239,8 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         uint32_t packed[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
-          if (bias) {
-            v0 += to_float(__ldg(bias + nb * kBlk + 2 * j));
-            v1 += to_float(__ldg(bias + nb * kBlk + 2 * j + 1));
-          }
+          const float2 bv = *reinterpret_cast<const float2*>(&s_bias[l * kBlk + 2 * j]);
+          const float v0 = __uint_as_float(r[2 * j]) + bv.x, v1 = __uint_as_float(r[2 * j + 1]) + bv.y;
           if constexpr (FMT == 0) {
             __half2 h = __floats2half2_rn(v0, v1);
             packed[j] = *reinterpret_cast<uint32_t*>(&h);
@@ -229,7 +249,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             packed[j] = *reinterpret_cast<uint32_t*>(&h);
           }
         }
-        uint4* dst = reinterpret_cast<uint4*>(crow + nb * kBlk);
+        uint4* dst = reinterpret_cast<uint4*>(crow + (nb0 + l) * kBlk);
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
@@ -283,15 +303,6 @@ int launch_dsd(const BsmmParams& p, cudaStream_t st) {
   return launch_status();
 }
 
-int panel_width() {
-  static int np = [] {
-    const char* e = std::getenv("SPARTA_TC_PANEL");
-    const int v = e ? std::atoi(e) : 16;
-    return v == 8 ? 8 : 16;
-  }();
-  return np;
-}
-
 }  // namespace
 
 bool bsmm_tc_available() { return true; }
@@ -301,7 +312,7 @@ bool bsmm_tc_supported(const BsmmParams& p) {
   if (p.dtype != SPARTA_F16 && p.dtype != SPARTA_BF16) return false;
   if (p.BM != kTileM || p.BK != kBlk || p.BN != kBlk) return false;
   if (p.M % kTileM || p.K % kBlk || p.N % kBlk) return false;
-  if (p.K / kBlk > kMaxRowBlocks || p.n_index_sets != 1 || p.val_stride_blocks <= 0) return false;
+  if (p.K / kBlk > kMaxKb || p.n_index_sets != 1 || p.val_stride_blocks <= 0) return false;
   if ((long long)p.batch * p.val_stride_blocks * kBlk > 0x7fffffffll) return false;
   if ((long long)p.batch * p.M > 0x7fffffffll || p.batch > 65535 || p.M / kTileM > 65535) return false;
   if (!aligned(p.A, 16) || !aligned(p.B, 16) || !aligned(p.C, 16)) return false;
@@ -310,8 +321,8 @@ bool bsmm_tc_supported(const BsmmParams& p) {
 
 int bsmm_tc(const BsmmParams& p, cudaStream_t st) {
   const int fmt = p.dtype == SPARTA_F16 ? 0 : 1;
-  if (panel_width() == 8) return fmt == 0 ? launch_dsd<8, 0>(p, st) : launch_dsd<8, 1>(p, st);
-  return fmt == 0 ? launch_dsd<16, 0>(p, st) : launch_dsd<16, 1>(p, st);
+  return fmt == 0 ? launch_dsd<kPanel, 0>(p, st) : launch_dsd<kPanel, 1>(p, st);
 }
 
 }  // namespace sparta
+
