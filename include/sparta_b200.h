@@ -87,6 +87,21 @@ int sparta_bcs_build(const uint8_t* mask, int n_masks, int H, int W, int BH, int
                      int64_t idx_capacity, int32_t* nnz, int32_t* uniform, int32_t* h_nnz,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* Index build without a caller-supplied workspace (no counterpart in the reference, which allocates
+ * freely with torch).  For callers that cannot allocate device memory -- a serving loop with a memory
+ * pool frozen after start-up, a plug-in whose host framework forbids cudaMalloc on its threads, a mask
+ * update issued while another thread holds the allocator lock.  Same arguments and results as
+ * sparta_bcs_build minus workspace / h_nnz; the scratch is a fixed SPARTA_BCS_STATIC_SCRATCH_BYTES array
+ * inside the library, one per device.  Requests whose sparta_bcs_build_workspace_bytes() exceeds it
+ * return SPARTA_ERR_WORKSPACE.  The first call on a device resolves the array's address: make it before
+ * any stream capture.  Calls on one device share the array: do not let two of them overlap on the GPU. */
+#define SPARTA_BCS_STATIC_SCRATCH_BYTES (1 << 20)
+
+int sparta_bcs_build_static(const uint8_t* mask, int n_masks, int H, int W, int BH, int BW,
+                            int want_bcsr, int want_bcsc,
+                            int32_t* row_ptr, int32_t* bcsr_idx, int32_t* col_ptr, void* bcsc_idx,
+                            int64_t idx_capacity, int32_t* nnz, int32_t* uniform, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Dense <-> compressed values.
  * Replaces BCSFunctionContext.convert / inverse (sparta/tesa/block_compressed.py:311-358) and

@@ -52,6 +52,9 @@ SIGNATURES = {
     'sparta_bcs_build': (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_size_t, c_void_p]),
+    'sparta_bcs_build_static': (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                        c_void_p]),
     'sparta_bcs_gather': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_int64, c_int64, c_void_p]),
     'sparta_bcs_scatter': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,

@@ -300,3 +300,76 @@ extern "C" int sparta_bcs_build(const uint8_t* mask, int n_masks, int H, int W, 
   }
   return SPARTA_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Index build for callers that cannot allocate device memory.
+//
+// sparta_bcs_build() needs a workspace from its caller.  Some callers have no way to get one: a
+// serving loop whose memory pool is frozen after start-up, a plug-in running under a host framework
+// that forbids cudaMalloc on its threads (the call synchronises the device and can fail once memory
+// is fragmented), or a mask update issued from a callback while another thread holds the framework's
+// allocator lock.  For them the scratch lives in the library image itself: a fixed array in device
+// global memory that every GPU loading this library carries until the process exits.
+//
+// Limits and rules
+//   * the array is SPARTA_BCS_STATIC_SCRATCH_BYTES (1 MiB) per device; a mask set whose
+//     sparta_bcs_build_workspace_bytes() is larger is refused with SPARTA_ERR_WORKSPACE
+//     (1 MiB covers e.g. 32 masks of 2048 x 2048 or one mask of 8192 x 8192 at 32 x 32 blocks);
+//   * the first call on a device looks up the array's device address (cudaGetSymbolAddress) with that
+//     device current; make that first call before starting any stream capture;
+//   * all calls on a device share the one array and it keeps whatever the previous call left, so the
+//     ticket words are cleared on the stream before each launch; two calls that may run on the GPU at
+//     the same time (different streams, different host threads) race on it -- serialise them;
+//   * nothing here calls cudaMalloc, cudaFree or any allocating routine.
+// ---------------------------------------------------------------------------------------------------
+#include <mutex>
+
+namespace {
+
+static __device__ __align__(256) unsigned char g_bcs_static_scratch[SPARTA_BCS_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_scratch_addr[kMaxDevices] = {nullptr};
+std::mutex g_scratch_mutex;
+
+// Device address of the static scratch on the current device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel may use, hence the symbol lookup (once per device).
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return SPARTA_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_bcs_static_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (!p) return SPARTA_ERR_DRIVER;
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return SPARTA_OK;
+}
+
+}  // namespace
+
+extern "C" int sparta_bcs_build_static(const uint8_t* mask, int n_masks, int H, int W, int BH, int BW,
+                                       int want_bcsr, int want_bcsc, int32_t* row_ptr, int32_t* bcsr_idx,
+                                       int32_t* col_ptr, void* bcsc_idx, int64_t idx_capacity, int32_t* nnz,
+                                       int32_t* uniform, void* stream) {
+  if (n_masks <= 0 || H <= 0 || W <= 0) return SPARTA_ERR_BAD_ARG;
+  if (!valid_bcs_block(BH) || !valid_bcs_block(BW) || H % BH || W % BW) return SPARTA_ERR_SHAPE;
+  const size_t need = sparta_bcs_build_workspace_bytes(n_masks, H, W, BH, BW);
+  if (need == 0 || need > (size_t)SPARTA_BCS_STATIC_SCRATCH_BYTES) return SPARTA_ERR_WORKSPACE;
+  void* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc != SPARTA_OK) return rc;
+  // the ticket words sit at the end of the workspace layout and must read zero when the kernel starts
+  const size_t blocks = (size_t)n_masks * (H / BH) * (W / BW);
+  const size_t ticket_off = align_up(blocks, 256) + align_up(blocks * 4, 256);
+  cudaError_t e = cudaMemsetAsync(static_cast<unsigned char*>(scratch) + ticket_off, 0,
+                                  align_up((size_t)n_masks * 4, 256), static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return sparta_bcs_build(mask, n_masks, H, W, BH, BW, want_bcsr, want_bcsc, row_ptr, bcsr_idx, col_ptr,
+                          bcsc_idx, idx_capacity, nnz, uniform, nullptr, scratch, need, stream);
+}
