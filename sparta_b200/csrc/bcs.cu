@@ -64,8 +64,103 @@ __device__ void block_scan_inplace(int32_t* p, int n, int32_t* s_part) {
   __syncthreads();
 }
 
+constexpr int kOccSmem = 16384;  // blocks of one mask held in shared memory by the compaction phase
+constexpr int kPtrSmem = 2048;   // block rows / columns whose pointer array fits in shared memory
+
+// Counts, prefix sum and ordered compaction for mask b, run by the whole (last) CTA.
+// SMEM: occupancy bytes and the pointer array live in shared memory; otherwise in global memory.
+template <bool SMEM>
+__device__ void phase2(const BcsParams& p, int b, const uint8_t* occ, int32_t* s_ptr, int32_t* s_part,
+                       int* s_nonuniform) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int R = p.R, Cn = p.Cn;
+  auto occ_at = [&](size_t i) -> int { return SMEM ? occ[i] : __ldcg(&occ[i]); };
+  int32_t* rank = p.rank ? p.rank + (size_t)b * R * Cn : nullptr;
+  int nonuni = 0;
+  if (p.want_bcsr) {
+    int32_t* g_row_ptr = p.row_ptr + (size_t)b * (R + 1);
+    int32_t* row_ptr = SMEM ? s_ptr : g_row_ptr;
+    int32_t* out = p.bcsr_idx + (size_t)b * p.idx_capacity;
+    if (threadIdx.x == 0) row_ptr[0] = 0;
+    for (int r = warp; r < R; r += kWarps) {
+      int cnt = 0;
+      for (int c = lane; c < Cn; c += 32) {
+        const int o = occ_at((size_t)r * Cn + c);
+        cnt += o & 1;
+        nonuni |= o & 2;
+      }
+      cnt = warp_sum_int(cnt);
+      if (lane == 0) row_ptr[r + 1] = cnt;
+    }
+    __syncthreads();
+    block_scan_inplace(row_ptr, R, s_part);
+    if (SMEM)
+      for (int r = threadIdx.x; r <= R; r += kThreads) g_row_ptr[r] = row_ptr[r];
+    for (int r = warp; r < R; r += kWarps) {
+      int off = row_ptr[r];
+      for (int c0 = 0; c0 < Cn; c0 += 32) {
+        const int c = c0 + lane;
+        const int f = (c < Cn) ? (occ_at((size_t)r * Cn + c) & 1) : 0;
+        const unsigned bal = __ballot_sync(0xffffffffu, f);
+        if (f) {
+          const int pos = off + __popc(bal & ((1u << lane) - 1u));
+          if (pos < p.idx_capacity) out[pos] = (r << 16) | c;
+          if (rank) rank[(size_t)r * Cn + c] = pos;
+        }
+        off += __popc(bal);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) p.nnz[b] = row_ptr[R];
+    __syncthreads();
+  }
+  if (p.want_bcsc) {
+    int32_t* g_col_ptr = p.col_ptr + (size_t)b * (Cn + 1);
+    int32_t* col_ptr = SMEM ? s_ptr : g_col_ptr;
+    if (threadIdx.x == 0) col_ptr[0] = 0;
+    for (int c = threadIdx.x; c < Cn; c += kThreads) {
+      int cnt = 0;
+      for (int r = 0; r < R; ++r) {
+        const int o = occ_at((size_t)r * Cn + c);
+        cnt += o & 1;
+        nonuni |= o & 2;
+      }
+      col_ptr[c + 1] = cnt;
+    }
+    __syncthreads();
+    block_scan_inplace(col_ptr, Cn, s_part);
+    if (SMEM)
+      for (int c = threadIdx.x; c <= Cn; c += kThreads) g_col_ptr[c] = col_ptr[c];
+    const bool both = p.want_bcsr != 0;
+    int32_t* out32 = reinterpret_cast<int32_t*>(p.bcsc_idx) + (size_t)b * p.idx_capacity;
+    long long* out64 = reinterpret_cast<long long*>(p.bcsc_idx) + (size_t)b * p.idx_capacity;
+    for (int c = threadIdx.x; c < Cn; c += kThreads) {
+      int pos = col_ptr[c];
+      for (int r = 0; r < R; ++r) {
+        if (occ_at((size_t)r * Cn + c) & 1) {
+          if (pos < p.idx_capacity) {
+            if (both)
+              out64[pos] = ((long long)rank[(size_t)r * Cn + c] << 32) | (long long)((c << 16) | r);
+            else
+              out32[pos] = (c << 16) | r;
+          }
+          ++pos;
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !p.want_bcsr) p.nnz[b] = col_ptr[Cn];
+  }
+  if (nonuni) *s_nonuniform = 1;  // benign race: every writer stores 1
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (p.uniform) p.uniform[b] = *s_nonuniform ? 0 : 1;
+    p.counters[b] = 0;  // leave the ticket ready for the next call
+  }
+}
+
 template <int VW>
-__global__ void __launch_bounds__(kThreads) bcs_build_kernel(BcsParams p) {
+__global__ void __launch_bounds__(kThreads, 4) bcs_build_kernel(BcsParams p) {
   constexpr int NWORD = VW / 4;
   const int b = blockIdx.y;
   const int lane = threadIdx.x & 31;
@@ -85,21 +180,34 @@ __global__ void __launch_bounds__(kThreads) bcs_build_kernel(BcsParams p) {
     for (int c = col0 + lane * VW; c < col0 + p.seg_w; c += 32 * VW) {
       if (c < p.W) {
         const uint8_t* src = row0 + c;
-        for (int y = 0; y < p.BH; y += 4) {  // BH is a multiple of 4: four loads in flight
-          if constexpr (VW == 16) {
-            uint4 v0 = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(y + 0) * p.W));
-            uint4 v1 = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(y + 1) * p.W));
-            uint4 v2 = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(y + 2) * p.W));
-            uint4 v3 = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(y + 3) * p.W));
-            any[0] |= v0.x | v1.x | v2.x | v3.x;
-            any[1] |= v0.y | v1.y | v2.y | v3.y;
-            any[2] |= v0.z | v1.z | v2.z | v3.z;
-            any[3] |= v0.w | v1.w | v2.w | v3.w;
-            zer[0] |= zero_bytes(v0.x) | zero_bytes(v1.x) | zero_bytes(v2.x) | zero_bytes(v3.x);
-            zer[1] |= zero_bytes(v0.y) | zero_bytes(v1.y) | zero_bytes(v2.y) | zero_bytes(v3.y);
-            zer[2] |= zero_bytes(v0.z) | zero_bytes(v1.z) | zero_bytes(v2.z) | zero_bytes(v3.z);
-            zer[3] |= zero_bytes(v0.w) | zero_bytes(v1.w) | zero_bytes(v2.w) | zero_bytes(v3.w);
-          } else {
+        if constexpr (VW == 16) {
+          const uint4* q = reinterpret_cast<const uint4*>(src);
+          const size_t pitch = (size_t)p.W / 16;
+          int y = 0;
+          for (; y + 8 <= p.BH; y += 8) {  // eight 16-byte loads in flight per lane
+            uint4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __ldg(q + (size_t)(y + i) * pitch);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              any[0] |= v[i].x; any[1] |= v[i].y; any[2] |= v[i].z; any[3] |= v[i].w;
+              zer[0] |= zero_bytes(v[i].x); zer[1] |= zero_bytes(v[i].y);
+              zer[2] |= zero_bytes(v[i].z); zer[3] |= zero_bytes(v[i].w);
+            }
+          }
+          for (; y < p.BH; y += 4) {  // BH = 4 (or the tail of 12, 20, ...: not reachable, BH is 2^n)
+            uint4 v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = __ldg(q + (size_t)(y + i) * pitch);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              any[0] |= v[i].x; any[1] |= v[i].y; any[2] |= v[i].z; any[3] |= v[i].w;
+              zer[0] |= zero_bytes(v[i].x); zer[1] |= zero_bytes(v[i].y);
+              zer[2] |= zero_bytes(v[i].z); zer[3] |= zero_bytes(v[i].w);
+            }
+          }
+        } else {
+          for (int y = 0; y < p.BH; y += 4) {  // BH is a multiple of 4: four loads in flight
             uint32_t v0 = __ldg(reinterpret_cast<const uint32_t*>(src + (size_t)(y + 0) * p.W));
             uint32_t v1 = __ldg(reinterpret_cast<const uint32_t*>(src + (size_t)(y + 1) * p.W));
             uint32_t v2 = __ldg(reinterpret_cast<const uint32_t*>(src + (size_t)(y + 2) * p.W));
@@ -151,81 +259,21 @@ __global__ void __launch_bounds__(kThreads) bcs_build_kernel(BcsParams p) {
   __threadfence();
 
   // ---------------- phase 2: scan + ordered compaction ----------------
+  // Small block grids (the usual case) are first copied into shared memory with one round of wide
+  // loads, so the counting / scanning / compaction below never waits on L2 again.
+  __shared__ __align__(16) uint8_t s_occ[kOccSmem];
+  __shared__ int32_t s_ptr[kPtrSmem + 1];
   const int R = p.R, Cn = p.Cn;
-  int32_t* rank = p.rank ? p.rank + (size_t)b * R * Cn : nullptr;
-  int nonuni = 0;
-  if (p.want_bcsr) {
-    int32_t* row_ptr = p.row_ptr + (size_t)b * (R + 1);
-    int32_t* out = p.bcsr_idx + (size_t)b * p.idx_capacity;
-    if (threadIdx.x == 0) row_ptr[0] = 0;
-    for (int r = warp; r < R; r += kWarps) {
-      int cnt = 0;
-      for (int c = lane; c < Cn; c += 32) {
-        const int o = __ldcg(&occ[(size_t)r * Cn + c]);
-        cnt += o & 1;
-        nonuni |= o & 2;
-      }
-      cnt = warp_sum_int(cnt);
-      if (lane == 0) row_ptr[r + 1] = cnt;
-    }
+  const bool fast = (size_t)R * Cn <= kOccSmem && R <= kPtrSmem && Cn <= kPtrSmem &&
+                    (((size_t)b * R * Cn) % 16 == 0);
+  if (fast) {
+    const int n16 = (R * Cn + 15) / 16;
+    for (int i = threadIdx.x; i < n16; i += kThreads)
+      reinterpret_cast<uint4*>(s_occ)[i] = __ldcg(reinterpret_cast<const uint4*>(occ) + i);
     __syncthreads();
-    block_scan_inplace(row_ptr, R, s_part);
-    for (int r = warp; r < R; r += kWarps) {
-      int off = row_ptr[r];
-      for (int c0 = 0; c0 < Cn; c0 += 32) {
-        const int c = c0 + lane;
-        const int f = (c < Cn) ? (__ldcg(&occ[(size_t)r * Cn + c]) & 1) : 0;
-        const unsigned bal = __ballot_sync(0xffffffffu, f);
-        if (f) {
-          const int pos = off + __popc(bal & ((1u << lane) - 1u));
-          if (pos < p.idx_capacity) out[pos] = (r << 16) | c;
-          if (rank) rank[(size_t)r * Cn + c] = pos;
-        }
-        off += __popc(bal);
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) p.nnz[b] = row_ptr[R];
-  }
-  if (p.want_bcsc) {
-    int32_t* col_ptr = p.col_ptr + (size_t)b * (Cn + 1);
-    if (threadIdx.x == 0) col_ptr[0] = 0;
-    for (int c = threadIdx.x; c < Cn; c += kThreads) {
-      int cnt = 0;
-      for (int r = 0; r < R; ++r) {
-        const int o = __ldcg(&occ[(size_t)r * Cn + c]);
-        cnt += o & 1;
-        nonuni |= o & 2;
-      }
-      col_ptr[c + 1] = cnt;
-    }
-    __syncthreads();
-    block_scan_inplace(col_ptr, Cn, s_part);
-    const bool both = p.want_bcsr != 0;
-    int32_t* out32 = reinterpret_cast<int32_t*>(p.bcsc_idx) + (size_t)b * p.idx_capacity;
-    long long* out64 = reinterpret_cast<long long*>(p.bcsc_idx) + (size_t)b * p.idx_capacity;
-    for (int c = threadIdx.x; c < Cn; c += kThreads) {
-      int pos = col_ptr[c];
-      for (int r = 0; r < R; ++r) {
-        if (__ldcg(&occ[(size_t)r * Cn + c]) & 1) {
-          if (pos < p.idx_capacity) {
-            if (both)
-              out64[pos] = ((long long)rank[(size_t)r * Cn + c] << 32) | (long long)((c << 16) | r);
-            else
-              out32[pos] = (c << 16) | r;
-          }
-          ++pos;
-        }
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0 && !p.want_bcsr) p.nnz[b] = col_ptr[Cn];
-  }
-  if (nonuni) s_nonuniform = 1;  // benign race: every writer stores 1
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    if (p.uniform) p.uniform[b] = s_nonuniform ? 0 : 1;
-    p.counters[b] = 0;  // leave the ticket ready for the next call
+    phase2<true>(p, b, s_occ, s_ptr, s_part, &s_nonuniform);
+  } else {
+    phase2<false>(p, b, occ, nullptr, s_part, &s_nonuniform);
   }
 }
 
@@ -280,9 +328,10 @@ extern "C" int sparta_bcs_build(const uint8_t* mask, int n_masks, int H, int W, 
   p.segs = (W + p.seg_w - 1) / p.seg_w;
   p.units_per_mask = R * p.segs;
 
-  // spread the units of all masks over every resident warp slot of the GPU (148 SMs x 64 warps)
+  // spread the units of all masks over the warps resident at once (148 SMs x 4 CTAs x 8 warps), so
+  // the grid is a single wave
   const long long total_units = (long long)n_masks * p.units_per_mask;
-  const long long warp_slots = (long long)kNumSMs * 64;
+  const long long warp_slots = (long long)kNumSMs * 4 * kWarps;
   const int units_per_warp = (int)((total_units + warp_slots - 1) / warp_slots);
   int ctas = (p.units_per_mask + kWarps * units_per_warp - 1) / (kWarps * units_per_warp);
   if (ctas < 1) ctas = 1;
