@@ -1,9 +1,462 @@
-// placeholder until the fused attention kernel lands
+// Fused block-sparse attention forward on tcgen05 / TMEM / TMA (fp16 / bf16, head dim 64 or 128,
+// 64 x 64 mask blocks):  O = softmax_mask(Q K^T * scale) V  over the kept blocks only.  The score
+// matrix lives in tensor memory and registers; it is never written to global memory.
+//
+// Replaces the three launches of SparseAttention.forward
+// (sparta/specializer/operators/sparse_attention.py:76-80): dds(Q, K^T) -> sparse softmax -> sdd(P, V).
+//
+// One CTA owns a 128-row Q tile = two block rows of the mask.  Its prologue merges the BCSR lists of
+// the two rows into a sorted list of K blocks with two presence bits each; K blocks are then taken
+// two at a time, so that both contractions run as full-width instructions:
+//   S[128, 128] = Q[128, D] . [K_a; K_b]^T           (tcgen05.mma M128 N128, D/16 of them)
+//   P = exp2(S * scale * log2e - m)  in registers, masked per row half and per element, -> smem
+//   O[128, D] += P[128, 128] . [V_a; V_b]             (tcgen05.mma M128 N=D, B operand MN-major)
+// Warps: 0-3 softmax (one row per thread, online max / sum with a lazy rescale of O: the running max
+// is only raised when it grows by more than 8 in log2 units), 4 TMA producer, 5 issues the Q.K^T
+// MMAs, 6 issues the P.V MMAs.  All mbarrier waits are bounded (status words of sparta_last_status).
+#include <type_traits>
+
 #include "bsmm.cuh"
-namespace sparta { bool attn_tc_available() { return false; } }
+#include "tc_common.cuh"
+
+namespace sparta {
+namespace {
+
+using namespace tc;
+
+constexpr int kBlk = 64;       // mask block edge
+constexpr int kTileM = 128;    // Q rows per CTA
+constexpr int kPair = 128;     // keys per step (two blocks)
+constexpr int kThreads = 224;
+constexpr int kMaxKb = 1024;   // K blocks per row (Ns <= 65536)
+constexpr float kRescaleThreshold = 8.f;
+
+struct AttnParams {
+  const int32_t* row_ptr;
+  const int32_t* idx;
+  const uint8_t* mask;  // [Nt, Ns] element mask or null
+  void* O;
+  float* lse;
+  int Nt, Ns, heads;
+  float scale_log2;     // scale * log2(e)
+  int32_t* status;
+};
+
+template <int D>
+struct Cfg {
+  static constexpr int kSBuf = D == 64 ? 1 : 2;      // score buffers in tensor memory
+  static constexpr int kKStages = D == 64 ? 1 : 2;
+  static constexpr int kVStages = 2;
+  static constexpr int kChunks = D / 64;             // 64-element (128-byte) chunks of the head dim
+  static constexpr int kQBytes = kTileM * D * 2;
+  static constexpr int kKVBytes = kPair * D * 2;     // one stage: two blocks
+  static constexpr int kPBytes = kTileM * kPair * 2;
+  static constexpr uint32_t kTmemCols = D == 64 ? 256 : 512;
+  static constexpr uint32_t kOCol = kSBuf * kPair;
+  static constexpr int kListBytes = kMaxKb * 2 + kMaxKb;  // ulist (uint16) + kmask (uint8)
+  static constexpr int kSmem = kQBytes + (kKStages + kVStages) * kKVBytes + kPBytes + kListBytes + 512 + 1024;
+};
+
+template <int D, int FMT>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, AttnParams p) {
+  using T = typename std::conditional<FMT == 0, __half, __nv_bfloat16>::type;
+  using C = Cfg<D>;
+  constexpr int kSBuf = C::kSBuf, kKStages = C::kKStages, kVStages = C::kVStages, kChunks = C::kChunks;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* k_s = q_s + C::kQBytes;
+  uint8_t* v_s = k_s + kKStages * C::kKVBytes;
+  uint8_t* p_s = v_s + kVStages * C::kKVBytes;
+  uint16_t* ulist = reinterpret_cast<uint16_t*>(p_s + C::kPBytes);  // (K block << 2) | presence bits
+  uint8_t* kmask = reinterpret_cast<uint8_t*>(ulist + kMaxKb);
+  uint8_t* ctl = kmask + kMaxKb;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(ctl);
+  uint64_t* k_full = q_full + 1;             // [kKStages]
+  uint64_t* k_empty = k_full + kKStages;     // [kKStages]
+  uint64_t* v_full = k_empty + kKStages;     // [kVStages]
+  uint64_t* v_empty = v_full + kVStages;     // [kVStages]
+  uint64_t* s_full = v_empty + kVStages;     // [kSBuf]
+  uint64_t* s_empty = s_full + kSBuf;        // [kSBuf]
+  uint64_t* p_full = s_empty + kSBuf;        // [1]
+  uint64_t* pv_done = p_full + 1;            // [1]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_done + 1);
+  int* s_count = reinterpret_cast<int*>(tmem_holder + 1);
+  int* s_range = s_count + 1;                // [2]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.x, tile = blockIdx.y;
+  const int br0 = tile * 2;
+  const int ncb = p.Ns / kBlk;
+
+  // ------------------------------ prologue ------------------------------
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kKStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < kVStages; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int s = 0; s < kSBuf; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4); }
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    fence_mbar_init();
+    s_range[0] = p.row_ptr[br0];
+    s_range[1] = p.row_ptr[br0 + 2];
+  }
+  if (warp == 4 && lane == 0) {
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_v);
+  }
+  if (warp == 5) tmem_alloc<C::kTmemCols>(tmem_holder);
+  for (int k = threadIdx.x; k < ncb; k += kThreads) kmask[k] = 0;
+  __syncthreads();
+  // the two block rows are consecutive in the BCSR array: entry = (block row << 16) | K block
+  for (int e = s_range[0] + threadIdx.x; e < s_range[1]; e += kThreads) {
+    const int v = __ldg(p.idx + e);
+    atomicOr(reinterpret_cast<unsigned int*>(kmask + ((v & 0xffff) & ~3)),
+             (1u << ((v >> 16) - br0)) << (8 * ((v & 0xffff) & 3)));
+  }
+  __syncthreads();
+  if (warp == 0) {  // ordered compaction of the merged list
+    int n = 0;
+    for (int base = 0; base < ncb; base += 32) {
+      const int k = base + lane;
+      const int m = k < ncb ? kmask[k] : 0;
+      const unsigned bal = __ballot_sync(0xffffffffu, m != 0);
+      if (m) ulist[n + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>((k << 2) | m);
+      n += __popc(bal);
+    }
+    if (lane == 0) *s_count = n;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const int count = *s_count;
+  const int npairs = (count + 1) / 2;
+  const long long q_row0 = (long long)head * p.Nt + (long long)tile * kTileM;
+  const long long kv_row0 = (long long)head * p.Ns;
+
+  if (warp == 4) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0 && count > 0) {
+      mbar_arrive_expect_tx(q_full, C::kQBytes);
+      for (int c = 0; c < kChunks; ++c)
+        tma_load_2d(q_s + c * (kTileM * 128), &tm_q, c * 64, (int)q_row0, q_full);
+      bool ok = true;
+      for (int j = 0; j < npairs && ok; ++j) {
+        const int nblk = min(2, count - 2 * j);
+        const int ks = j % kKStages, vs = j % kVStages;
+        if (!mbar_wait(&k_empty[ks], ((j / kKStages) & 1) ^ 1)) { ok = false; break; }
+        mbar_arrive_expect_tx(&k_full[ks], nblk * kBlk * D * 2);
+        for (int b = 0; b < nblk; ++b) {
+          const int kb = ulist[2 * j + b] >> 2;
+          for (int c = 0; c < kChunks; ++c)
+            tma_load_2d(k_s + ks * C::kKVBytes + c * (kPair * 128) + b * (kBlk * 128), &tm_k, c * 64,
+                        (int)(kv_row0 + (long long)kb * kBlk), &k_full[ks]);
+        }
+        if (!mbar_wait(&v_empty[vs], ((j / kVStages) & 1) ^ 1)) { ok = false; break; }
+        mbar_arrive_expect_tx(&v_full[vs], nblk * kBlk * D * 2);
+        for (int b = 0; b < nblk; ++b) {
+          const int kb = ulist[2 * j + b] >> 2;
+          for (int c = 0; c < kChunks; ++c)
+            tma_load_2d(v_s + vs * C::kKVBytes + c * (kPair * 128) + b * (kBlk * 128), &tm_v, c * 64,
+                        (int)(kv_row0 + (long long)kb * kBlk), &v_full[vs]);
+        }
+      }
+      if (!ok) atomicExch(&p.status[0], 1);
+    }
+  } else if (warp == 5) {
+    // ------------------------------ S = Q K^T ------------------------------
+    const uint64_t desc_hi = make_smem_desc(0, 16, 1024, SW_128B);
+    const uint32_t q_lo = smem_u32(q_s) >> 4, k_lo = smem_u32(k_s) >> 4;
+    bool ok = count == 0 || mbar_wait(q_full, 0);
+    for (int j = 0; j < npairs && ok; ++j) {
+      const int nblk = min(2, count - 2 * j);
+      const int ks = j % kKStages, sb = j % kSBuf;
+      if (!mbar_wait(&k_full[ks], (j / kKStages) & 1)) { ok = false; break; }
+      if (!mbar_wait(&s_empty[sb], ((j / kSBuf) & 1) ^ 1)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint32_t idesc = make_idesc_f16(kTileM, nblk * kBlk, FMT, 0, 0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = ((kk / 4) * (kTileM * 128) + (kk % 4) * 32) >> 4;  // kTileM == kPair
+          umma_ss(tmem_base + sb * kPair, desc_hi | (q_lo + off),
+                  desc_hi | (k_lo + ((ks * C::kKVBytes) >> 4) + off), idesc, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[sb]);
+        umma_commit(&k_empty[ks]);
+      }
+      __syncwarp();
+    }
+    if (!ok && lane == 0) atomicExch(&p.status[1], 1);
+  } else if (warp == 6) {
+    // ------------------------------ O += P V ------------------------------
+    // P: K-major, two 64-key chunks of [128 rows x 128 B]; V: MN-major (head dim contiguous), 8 keys
+    // per 1024-byte group, 64-element chunks of the head dim kPair * 128 bytes apart.
+    const uint64_t p_desc_hi = make_smem_desc(0, 16, 1024, SW_128B);
+    const uint64_t v_desc_hi = make_smem_desc(0, kPair * 128, 1024, SW_128B);
+    const uint32_t p_lo = smem_u32(p_s) >> 4, v_lo = smem_u32(v_s) >> 4;
+    constexpr uint32_t idesc = make_idesc_f16(kTileM, D, FMT, 0, 1);
+    bool ok = true;
+    for (int j = 0; j < npairs && ok; ++j) {
+      const int nblk = min(2, count - 2 * j);
+      const int vs = j % kVStages;
+      if (!mbar_wait(&v_full[vs], (j / kVStages) & 1)) { ok = false; break; }
+      if (!mbar_wait(p_full, j & 1)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (lane == 0) {
+        for (int kk = 0; kk < nblk * (kBlk / 16); ++kk) {
+          const uint32_t a_off = ((kk / 4) * (kTileM * 128) + (kk % 4) * 32) >> 4;
+          const uint32_t b_off = (vs * C::kKVBytes + kk * 16 * 128) >> 4;
+          umma_ss(tmem_base + C::kOCol, p_desc_hi | (p_lo + a_off), v_desc_hi | (v_lo + b_off), idesc,
+                  (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&v_empty[vs]);
+        umma_commit(pv_done);
+      }
+      __syncwarp();
+    }
+    if (!ok && lane == 0) atomicExch(&p.status[2], 1);
+  } else {
+    // ------------------------------ softmax + epilogue (warps 0-3) ------------------------------
+    const int row = warp * 32 + lane;          // row of the Q tile == TMEM lane
+    const int half = row >> 6;                 // which of the two block rows
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const long long grow = (long long)tile * kTileM + row;  // row inside the head
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < npairs && ok; ++j) {
+      const int nblk = min(2, count - 2 * j);
+      const int sb = j % kSBuf;
+      const int e0 = ulist[2 * j], e1 = nblk > 1 ? ulist[2 * j + 1] : 0;
+      const bool have0 = (e0 >> half) & 1, have1 = (e1 >> half) & 1;
+      const int kb[2] = {e0 >> 2, e1 >> 2};
+      const bool have[2] = {have0, have1};
+      if (!mbar_wait(&s_full[sb], (j / kSBuf) & 1)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t s_addr = tmem_base + lane_base + sb * kPair;
+      // ---- pass 1: row maximum over the kept, unmasked scores ----
+      float mx = -INFINITY;
+      for (int b = 0; b < nblk; ++b) {
+        if (!have[b]) continue;  // warp-uniform: a warp lies inside one block row
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld_x32(s_addr + b * kBlk + h * 32, r);
+          tmem_ld_wait();
+          if (p.mask) {
+            const uint8_t* mrow = p.mask + grow * p.Ns + (long long)kb[b] * kBlk + h * 32;
+            const uint4 m0 = __ldg(reinterpret_cast<const uint4*>(mrow));
+            const uint4 m1 = __ldg(reinterpret_cast<const uint4*>(mrow) + 1);
+            const uint32_t mw[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if ((mw[i >> 2] >> (8 * (i & 3))) & 0xffu) mx = fmaxf(mx, __uint_as_float(r[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          }
+        }
+      }
+      const float m_new = mx * p.scale_log2;  // scale > 0
+      // ---- lazy rescale of the running state ----
+      float alpha = 1.f;
+      if (m_new > m_run + kRescaleThreshold || (m_run == -INFINITY && m_new > -INFINITY)) {
+        alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+        m_run = m_new;
+        l_run *= alpha;
+      }
+      // previous P V must be finished before P is overwritten or O is rescaled
+      if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_x32(tmem_base + lane_base + C::kOCol + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_x32(tmem_base + lane_base + C::kOCol + c * 32, r);
+        }
+        tmem_st_wait();
+      }
+      // ---- pass 2: P = exp2(S * scale * log2e - m) -> shared memory (K-major, 128-byte swizzle) ----
+      for (int b = 0; b < nblk; ++b) {
+        uint8_t* prow = p_s + b * (kTileM * 128) + row * 128;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t packed[16];
+          if (have[b]) {  // warp-uniform: tcgen05.ld needs the whole warp
+            uint32_t r[32];
+            tmem_ld_x32(s_addr + b * kBlk + h * 32, r);
+            tmem_ld_wait();
+            const bool dead = !(m_run > -INFINITY);  // every score of this row masked so far
+            uint32_t mw[8];
+            if (p.mask) {
+              const uint8_t* mrow = p.mask + grow * p.Ns + (long long)kb[b] * kBlk + h * 32;
+              const uint4 m0 = __ldg(reinterpret_cast<const uint4*>(mrow));
+              const uint4 m1 = __ldg(reinterpret_cast<const uint4*>(mrow) + 1);
+              mw[0] = m0.x; mw[1] = m0.y; mw[2] = m0.z; mw[3] = m0.w;
+              mw[4] = m1.x; mw[5] = m1.y; mw[6] = m1.z; mw[7] = m1.w;
+            }
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float p0 = exp2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_run));
+              float p1 = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_run));
+              if (p.mask) {
+                if (!((mw[(2 * i) >> 2] >> (8 * ((2 * i) & 3))) & 0xffu)) p0 = 0.f;
+                if (!((mw[(2 * i + 1) >> 2] >> (8 * ((2 * i + 1) & 3))) & 0xffu)) p1 = 0.f;
+              }
+              if (dead) p0 = p1 = 0.f;
+              if constexpr (FMT == 0) {
+                const __half2 hv = __floats2half2_rn(p0, p1);
+                packed[i] = *reinterpret_cast<const uint32_t*>(&hv);
+                const float2 back = __half22float2(hv);
+                sum += back.x + back.y;  // the sum uses the rounded values that enter P V
+              } else {
+                const __nv_bfloat162 hv = __floats2bfloat162_rn(p0, p1);
+                packed[i] = *reinterpret_cast<const uint32_t*>(&hv);
+                const float2 back = __bfloat1622float2(hv);
+                sum += back.x + back.y;
+              }
+            }
+            l_run += sum;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) packed[i] = 0;
+          }
+          // 32 keys = 64 bytes = four 16-byte chunks; chunk index XOR (row % 8) is the 128-byte swizzle
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int chunk = (h * 4 + q) ^ (row & 7);
+            *reinterpret_cast<uint4*>(prow + chunk * 16) =
+                make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+          }
+        }
+      }
+      // S may be overwritten, P may be read by the tensor core
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s_empty[sb]);
+        mbar_arrive(p_full);
+      }
+    }
+    // ---- epilogue: O / l -> global ----
+    if (ok && npairs > 0 && !mbar_wait(pv_done, (npairs - 1) & 1)) ok = false;
+    if (!ok && lane == 0) atomicExch(&p.status[3], 1);
+    tc_fence_after_sync();
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    T* orow = static_cast<T*>(p.O) + (q_row0 + row) * D;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t r[32];
+      if (npairs > 0 && ok) {
+        tmem_ld_x32(tmem_base + lane_base + C::kOCol + c * 32, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = 0;
+      }
+      uint32_t packed[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float v0 = __uint_as_float(r[2 * i]) * inv, v1 = __uint_as_float(r[2 * i + 1]) * inv;
+        if constexpr (FMT == 0) {
+          const __half2 hv = __floats2half2_rn(v0, v1);
+          packed[i] = *reinterpret_cast<const uint32_t*>(&hv);
+        } else {
+          const __nv_bfloat162 hv = __floats2bfloat162_rn(v0, v1);
+          packed[i] = *reinterpret_cast<const uint32_t*>(&hv);
+        }
+      }
+      uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+    }
+    if (p.lse) {
+      // natural-log sum of exponentials of the scaled scores (-inf for a fully masked row)
+      p.lse[(long long)head * p.Nt + grow] = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc<C::kTmemCols>(tmem_base);
+  }
+}
+
+template <int D, int FMT>
+int launch_attn(const void* Q, const void* K, const void* V, const AttnParams& p, int dtype, cudaStream_t st) {
+  using C = Cfg<D>;
+  CUtensorMap tm_q, tm_k, tm_v;
+  const uint64_t strides[1] = {(uint64_t)D * 2};
+  {
+    const uint64_t dims[2] = {(uint64_t)D, (uint64_t)p.heads * p.Nt};
+    const uint32_t box[2] = {64, kTileM};
+    int rc = make_tensor_map(&tm_q, Q, dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != SPARTA_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)D, (uint64_t)p.heads * p.Ns};
+    const uint32_t box[2] = {64, kBlk};
+    int rc = make_tensor_map(&tm_k, K, dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != SPARTA_OK) return rc;
+    rc = make_tensor_map(&tm_v, V, dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != SPARTA_OK) return rc;
+  }
+  auto kern = attn_fwd_tc_kernel<D, FMT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  dim3 grid(p.heads, p.Nt / kTileM);  // x = head: the heavy first tile of every head is scheduled first
+  kern<<<grid, kThreads, C::kSmem, st>>>(tm_q, tm_k, tm_v, p);
+  return launch_status();
+}
+
+}  // namespace
+
+bool attn_tc_available() { return true; }
+
+}  // namespace sparta
+
+using namespace sparta;
+
 extern "C" size_t sparta_attn_fwd_workspace_bytes(int, int, int, int, int) { return 0; }
-extern "C" int sparta_attn_fwd(const void*, const void*, const void*, void*, const int32_t*,
-                               const int32_t*, const int32_t*, const uint8_t*, float, int, int, int,
-                               int, int, int, float*, int32_t*, void*, size_t, void*) {
-  return SPARTA_ERR_UNSUPPORTED;
+
+extern "C" int sparta_attn_fwd(const void* Q, const void* K, const void* V, void* O, const int32_t* row_ptr,
+                               const int32_t* bcsr_idx, const int32_t* nnz, const uint8_t* mask, float scale,
+                               int heads, int Nt, int Ns, int D, int BLK, int dtype, float* lse,
+                               int32_t* status, void* workspace, size_t workspace_bytes, void* stream) {
+  (void)nnz; (void)workspace; (void)workspace_bytes;
+  if (!Q || !K || !V || !O || !row_ptr || !bcsr_idx || heads <= 0 || Nt <= 0 || Ns <= 0) return SPARTA_ERR_BAD_ARG;
+  if (dtype != SPARTA_F16 && dtype != SPARTA_BF16) return SPARTA_ERR_UNSUPPORTED;
+  if (BLK != kBlk || (D != 64 && D != 128)) return SPARTA_ERR_UNSUPPORTED;
+  if (Nt % kTileM || Ns % kBlk) return SPARTA_ERR_SHAPE;
+  if (Ns / kBlk > kMaxKb || Nt / kTileM > 65535 || !(scale > 0.f)) return SPARTA_ERR_UNSUPPORTED;
+  if ((long long)heads * Nt > 0x7fffffffll || (long long)heads * Ns > 0x7fffffffll) return SPARTA_ERR_SHAPE;
+  if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16)) return SPARTA_ERR_ALIGN;
+  if (mask && (!aligned(mask, 16) || Ns % 16)) return SPARTA_ERR_ALIGN;
+  AttnParams p;
+  p.row_ptr = row_ptr; p.idx = bcsr_idx; p.mask = mask; p.O = O; p.lse = lse;
+  p.Nt = Nt; p.Ns = Ns; p.heads = heads;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status ? status : tc::device_status_ptr();
+  if (!p.status) return SPARTA_ERR_DRIVER;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int fmt = dtype == SPARTA_F16 ? 0 : 1;
+  if (D == 64) return fmt == 0 ? launch_attn<64, 0>(Q, K, V, p, dtype, st) : launch_attn<64, 1>(Q, K, V, p, dtype, st);
+  return fmt == 0 ? launch_attn<128, 0>(Q, K, V, p, dtype, st) : launch_attn<128, 1>(Q, K, V, p, dtype, st);
 }

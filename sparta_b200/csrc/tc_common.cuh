@@ -13,8 +13,13 @@ namespace tc {
 // ---------------------------------------------------------------------------------------------
 // device side
 // ---------------------------------------------------------------------------------------------
-constexpr uint32_t kWaitPolls = 1u << 22;  // try_wait polls before a wait gives up (each poll blocks
-                                           // for a hardware time slice, so this is seconds)
+constexpr unsigned long long kWaitNanos = 50ull * 1000 * 1000;  // a wait gives up after 50 ms
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -47,11 +52,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the phase did not complete within kWaitPolls polls.
+// Bounded wait: false when the phase did not complete within kWaitNanos.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitPolls; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > kWaitNanos) return false;
+  }
 }
 
 // 2-D TMA tile load: coordinates (x = innermost, y) in elements; completes `bytes` on `bar`.

@@ -124,6 +124,8 @@ class SparseAttention(OperatorBase):
                  sm.get('BLOCK_SIZE_W_VALUE'), out.get('BLOCK_SIZE_M_VALUE'), out.get('BLOCK_SIZE_K_VALUE')]
         if any(s != FUSED_BLOCK for s in sizes):
             return False
+        if self._Nt % (2 * FUSED_BLOCK) or self._Ns % FUSED_BLOCK or self._Ns // FUSED_BLOCK > 1024:
+            return False
         return _lib.lib().sparta_tile_table(_lib.OP_ATTENTION, _lib.DTYPE_CODE[query.dtype], None, 0) > 0
 
     def build(self, config: Dict[str, Any], sample_inputs: List[torch.Tensor]):

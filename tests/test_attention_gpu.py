@@ -82,3 +82,62 @@ def test_half_precision_attention_band_mask(dtype, E, fused):
     torch.testing.assert_close(out.float().cpu(), target, atol=2e-2, rtol=2e-2)
     if fused == 'auto' and op._use_fused:
         assert op.fused_status() == [0, 0, 0, 0]
+
+
+def _fused_case(dtype, E, heads, Nt, Ns, mask, seed=5, qscale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    q = (torch.randn((heads, Nt, E), generator=g) * qscale).to(dtype)
+    k = torch.randn((heads, Ns, E), generator=g).to(dtype)
+    v = torch.randn((heads, Ns, E), generator=g).to(dtype)
+    op = SparseAttention(mask=mask.cuda(), fused=True)
+    op.build(config=params(64), sample_inputs=[q.cuda(), k.cuda(), v.cuda()])
+    assert op._use_fused
+    out = op(q.cuda(), k.cuda(), v.cuda())
+    assert op.fused_status() == [0, 0, 0, 0]
+    target = oracle.attention_reference(q.float(), k.float(), v.float(), mask)
+    torch.testing.assert_close(out.float().cpu(), target, atol=2e-2, rtol=2e-2)
+    return op, (q, k, v)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('E', [64, 128])
+def test_fused_attention_edge_masks(dtype, E):
+    """Fused kernel: empty block rows, a single block, odd merged lists, rectangular masks."""
+    g = torch.Generator().manual_seed(9)
+    # rectangular, random blocks, one block row without any block and one Q tile without any block
+    mask = oracle.block_mask((512, 768), (64, 64), 0.6, generator=g)
+    mask[64:128] = 0
+    mask[256:384] = 0
+    _fused_case(dtype, E, 2, 512, 768, mask)
+    # exactly one kept block
+    one = torch.zeros((256, 256), dtype=torch.uint8)
+    one[128:192, 64:128] = 1
+    _fused_case(dtype, E, 1, 256, 256, one)
+    # fully dense
+    _fused_case(dtype, E, 1, 256, 384, torch.ones((256, 384), dtype=torch.uint8))
+
+
+@pytest.mark.parametrize('E', [64, 128])
+def test_fused_attention_element_mask_and_large_scores(E):
+    """8x8-granular mask inside 64x64 blocks (element masking in the kernel) and scores whose running
+    maximum keeps growing (exercises the rescale of the accumulator)."""
+    g = torch.Generator().manual_seed(10)
+    mask = oracle.block_mask((256, 512), (8, 8), 0.9, generator=g)
+    mask[40:48] = 0  # rows that are fully masked inside kept blocks
+    op, _ = _fused_case(torch.float16, E, 2, 256, 512, mask)
+    assert not op.get_sparse_indexes().block_uniform
+    dense = torch.ones((256, 1024), dtype=torch.uint8)
+    _fused_case(torch.float16, E, 1, 256, 1024, dense, seed=11, qscale=6.0)
+
+
+def test_fused_attention_dynamic_mask():
+    g = torch.Generator().manual_seed(12)
+    mask = oracle.block_mask((256, 256), (64, 64), 0.5, generator=g)
+    op, (q, k, v) = _fused_case(torch.float16, 64, 2, 256, 256, mask)
+    for seed in range(2):
+        g2 = torch.Generator().manual_seed(seed)
+        mask = oracle.block_mask((256, 256), (64, 64), 0.5, generator=g2)
+        op.update_mask(mask.cuda())
+        out = op(q.cuda(), k.cuda(), v.cuda())
+        target = oracle.attention_reference(q.float(), k.float(), v.float(), mask)
+        torch.testing.assert_close(out.float().cpu(), target, atol=2e-2, rtol=2e-2)
