@@ -1,0 +1,79 @@
+"""Sharding of the block-sparse operators across the GPUs of one box.
+
+The path has no exchange step: attention shards by batch x head (the leading dimension of
+``[B*H, N, E]`` tensors), SparseLinear by token rows; masks, indexes and weights are replicated, every
+rank builds its indexes locally.  The only collective offered is an optional all-gather of the
+outputs (NCCL over NVLink through ``torch.distributed``; gloo works for CPU tests).  The reference has
+no multi-GPU code; this module is an extension.
+"""
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(total: int, world_size: int, rank: int, multiple: int = 1) -> Tuple[int, int]:
+    """Contiguous ``[begin, end)`` of ``total`` units owned by ``rank``.
+
+    Units are dealt out in groups of ``multiple`` (e.g. the block height for token rows, so that a
+    shard never cuts a block row); earlier ranks take the remainder groups.  Raises ``ValueError`` when
+    ``total`` is not a multiple of ``multiple`` or a rank would be left without work.
+    """
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError(f'bad rank {rank} for world size {world_size}')
+    if multiple < 1 or total % multiple:
+        raise ValueError(f'{total} units cannot be split in groups of {multiple}')
+    groups = total // multiple
+    if groups < world_size:
+        raise ValueError(f'{groups} groups of {multiple} units cannot feed {world_size} ranks')
+    base, extra = divmod(groups, world_size)
+    begin = rank * base + min(rank, extra)
+    end = begin + base + (1 if rank < extra else 0)
+    return begin * multiple, end * multiple
+
+
+def shard_heads(*tensors: torch.Tensor, world_size: int, rank: int):
+    """Slices of ``[B*H, N, E]`` tensors along the batch x head dimension for this rank."""
+    lo, hi = shard_bounds(tensors[0].shape[0], world_size, rank)
+    out = tuple(t[lo:hi] for t in tensors)
+    return out if len(out) > 1 else out[0]
+
+
+def shard_rows(x: torch.Tensor, world_size: int, rank: int, block_rows: int = 1) -> torch.Tensor:
+    """Token-row slice of a ``[tokens, features]`` activation; ``block_rows`` keeps shards aligned to
+    the row tile of the kernel (and to the block height of an output mask)."""
+    lo, hi = shard_bounds(x.shape[0], world_size, rank, block_rows)
+    return x[lo:hi]
+
+
+def shard_row_mask(mask: torch.Tensor, world_size: int, rank: int, block_rows: int) -> torch.Tensor:
+    """The rows of an input / output mask ``[tokens, features]`` that belong to this rank's tokens."""
+    lo, hi = shard_bounds(mask.shape[0], world_size, rank, block_rows)
+    return mask[lo:hi].contiguous()
+
+
+def all_gather_outputs(local: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """Concatenate the ranks' outputs along dimension 0 (every rank gets the full tensor).
+
+    Shards may differ in size along dimension 0 by one group; equal shards use a single
+    ``all_gather_into_tensor``.
+    """
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return local
+    world = dist.get_world_size(group)
+    local = local.contiguous()
+    sizes = torch.zeros(world, dtype=torch.int64, device=local.device)
+    sizes[dist.get_rank(group)] = local.shape[0]
+    dist.all_reduce(sizes, group=group)
+    sizes = sizes.tolist()
+    if len(set(sizes)) == 1:
+        out = torch.empty((world * sizes[0],) + local.shape[1:], dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out, local, group=group)
+        return out
+    # uneven shards: pad to the largest, gather once, drop the padding
+    most = max(sizes)
+    padded = torch.zeros((most,) + local.shape[1:], dtype=local.dtype, device=local.device)
+    padded[:local.shape[0]] = local
+    out = torch.empty((world * most,) + local.shape[1:], dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, padded, group=group)
+    return torch.cat([out[r * most:r * most + n] for r, n in enumerate(sizes)], dim=0)
