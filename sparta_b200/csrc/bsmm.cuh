@@ -28,8 +28,14 @@ struct BsmmParams {
 int bsmm_simt(const BsmmParams& p, cudaStream_t st);
 
 // tcgen05 kernels: return SPARTA_ERR_UNSUPPORTED when the configuration is outside their coverage.
-bool bsmm_tc_supported(const BsmmParams& p);
-int bsmm_tc(const BsmmParams& p, cudaStream_t st);
+bool dsd_tc_supported(const BsmmParams& p);
+int dsd_tc_launch(const BsmmParams& p, cudaStream_t st);
+bool dds_tc_supported(const BsmmParams& p);
+int dds_tc_launch(const BsmmParams& p, cudaStream_t st);
+inline bool bsmm_tc_supported(const BsmmParams& p) { return dsd_tc_supported(p) || dds_tc_supported(p); }
+inline int bsmm_tc(const BsmmParams& p, cudaStream_t st) {
+  return p.mode == MODE_DDS ? dds_tc_launch(p, st) : dsd_tc_launch(p, st);
+}
 
 // whether the tcgen05 matmul / fused attention kernels are compiled into this build
 bool bsmm_tc_available();

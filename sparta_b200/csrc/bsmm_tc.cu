@@ -307,7 +307,7 @@ int launch_dsd(const BsmmParams& p, cudaStream_t st) {
 
 bool bsmm_tc_available() { return true; }
 
-bool bsmm_tc_supported(const BsmmParams& p) {
+bool dsd_tc_supported(const BsmmParams& p) {
   if (p.mode != MODE_DSD || !p.trans_b || p.trans_a || !p.compressed || p.idx_is_64) return false;
   if (p.dtype != SPARTA_F16 && p.dtype != SPARTA_BF16) return false;
   if (p.BM != kTileM || p.BK != kBlk || p.BN != kBlk) return false;
@@ -319,7 +319,7 @@ bool bsmm_tc_supported(const BsmmParams& p) {
   return true;
 }
 
-int bsmm_tc(const BsmmParams& p, cudaStream_t st) {
+int dsd_tc_launch(const BsmmParams& p, cudaStream_t st) {
   const int fmt = p.dtype == SPARTA_F16 ? 0 : 1;
   return fmt == 0 ? launch_dsd<kPanel, 0>(p, st) : launch_dsd<kPanel, 1>(p, st);
 }

@@ -66,3 +66,58 @@ def test_dsd_tcgen05_is_deterministic():
     a = kernel(*args)
     c = kernel(*args)
     assert torch.equal(a, c)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('trans_B', [True, False])
+@pytest.mark.parametrize('compressed', [True, False])
+@pytest.mark.parametrize('batch,M,K,N,sparsity,biased', [
+    (1, 128, 64, 32, 0.0, False),      # one tile, one column, one K chunk
+    (2, 256, 256, 320, 0.5, True),     # two groups (10 columns), batch, bias
+    (1, 512, 1024, 1024, 0.9, False),  # sparse: most groups empty
+    (1, 384, 128, 2048, 0.97, True),   # row tiles without any block
+])
+def test_dds_tcgen05(dtype, trans_B, compressed, batch, M, K, N, sparsity, biased):
+    g = torch.Generator().manual_seed(M + K + N)
+    A = torch.randn((batch, M, K), generator=g).to(dtype)
+    B = (torch.randn((batch, N, K) if trans_B else (batch, K, N), generator=g) * 0.1).to(dtype)
+    bias = torch.randn((batch, N), generator=g).to(dtype) if biased else None
+    mask = oracle.block_mask((M, N), (32, 32), sparsity, generator=g)
+    if M >= 384:
+        mask[128:256] = 0
+    kernel = SparTASparseMatMulKernel(mode='dds', biased=biased, transpose_A=False, transpose_B=trans_B,
+                                      compressed=compressed)
+    kernel.ports['C'].set_mask(mask.cuda())
+    kernel.set_shape(batch, M, K, N)
+    cfg = {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': 32, 'BLOCK_SIZE_K_VALUE': 64, 'BLOCK_SIZE_N_VALUE': 32}
+    kernel.compile({**cfg, '_family': 'tcgen05'})
+    ix = kernel.ports['C'].indexes
+    args = [A.cuda(), B.cuda()] + ([bias.cuda()] if biased else [])
+    out = kernel(*args)
+    assert _lib.last_status() == [0, 0, 0, 0]
+    dense = ix.inverse(out) if compressed else out
+    expect = oracle.matmul_reference(A.float(), B.float(), bias.float() if biased else None, mask, 'dds',
+                                     False, trans_B, (32, 32))
+    torch.testing.assert_close(dense.float().cpu(), expect, **TOL)
+    kernel.compile({**cfg, '_family': 'simt'})
+    ref = kernel(*args)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+def test_dds_tcgen05_per_batch_masks():
+    from sparta_b200.nn import SparseBatchMatMul
+    batch, M, K, N = 4, 256, 128, 512
+    g = torch.Generator().manual_seed(21)
+    A = torch.randn((batch, M, K), generator=g).half()
+    B = torch.randn((batch, K, N), generator=g).half()
+    masks = torch.stack([oracle.block_mask((M, N), (32, 32), 0.85, generator=g) for _ in range(batch)]).cuda()
+    op = SparseBatchMatMul(C_mask=masks, compressed=True, capacity=96)
+    op.build({'forward:C': {'_impl': 'sparta', '_family': 'tcgen05', 'BLOCK_SIZE_M_VALUE': 32,
+                            'BLOCK_SIZE_K_VALUE': 64, 'BLOCK_SIZE_N_VALUE': 32}},
+             sample_inputs=[A.cuda(), B.cuda()])
+    op.set_dynamic(True)
+    out = op(A.cuda(), B.cuda())
+    assert _lib.last_status() == [0, 0, 0, 0]
+    ix = op.get_sparse_indexes('C')
+    full = torch.bmm(A.float(), B.float())
+    torch.testing.assert_close(ix.inverse(out).float().cpu(), full * masks.cpu().float(), **TOL)
