@@ -1,6 +1,6 @@
 """Benchmark of the block-sparse operator path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras | --extras LIST]
 
 One step = one pass of the hot path over one batch of seeded synthetic input.  The headline workload
 is SparseLinear fp16, x[4096 tokens, 4096] . W[4096, 4096]^T + b with a 32x32-block weight mask at 75 %
@@ -182,7 +182,7 @@ def build_linear(device, sparsity, mode='dsd', tokens=TOKENS):
     return dict(op=op, fn=fn, x=x, w=w, b=b, mask=mask, xd=xd, nnz=nnz, flops=flops, bytes=bytes_)
 
 
-def run_extras(device, peaks, flush):
+def run_extras(device, peaks, flush, only=None):
     """Secondary measurements (each: 3 warm-ups, 10 timed steps, L2 flushed between steps)."""
     import sparta_b200 as sparta
     from oracle import oracle
@@ -191,7 +191,8 @@ def run_extras(device, peaks, flush):
     def timed(fn, steps=10, do_flush=True):
         return time_steps(fn, steps, 3, flush if do_flush else (lambda: None)) / steps
 
-    for mode in ('dsd', 'dds'):
+    want = lambda name: only is None or name in only
+    for mode in (('dsd', 'dds') if want('linear') else ()):
         for sp in (0.75, 0.9, 0.95):
             if mode == 'dsd' and sp == SPARSITY:
                 continue
@@ -209,6 +210,8 @@ def run_extras(device, peaks, flush):
 
     # fused sparse attention forward: B4 H16 S4096 D64 fp16, band + global + 5 % random 64x64 blocks
     try:
+        if not want('attention'):
+            raise KeyError('skipped')
         heads, S, D = 64, 4096, 64
         g = torch.Generator().manual_seed(2024)
         q, k, v = (torch.randn((heads, S, D), generator=g).half().to(device) for _ in range(3))
@@ -229,6 +232,8 @@ def run_extras(device, peaks, flush):
 
     # mask -> BCSR on the GPU: 32 masks of 2048 x 2048, 32x32 blocks, 90 % sparse
     try:
+        if not want('convert'):
+            raise KeyError('skipped')
         gdev = torch.Generator(device=device).manual_seed(7)
         coarse = (torch.rand((32, 64, 64), device=device, generator=gdev) > 0.9).to(torch.uint8)
         masks = coarse.repeat_interleave(32, 1).repeat_interleave(32, 2).contiguous()
@@ -261,6 +266,8 @@ def run_extras(device, peaks, flush):
 
     # README workload: fp32, 1024^3, 8x8-block weight mask at 90 %
     try:
+        if not want('readme'):
+            raise KeyError('skipped')
         g = torch.Generator().manual_seed(2022)
         x = torch.rand((1024, 1024), generator=g).to(device)
         w = torch.rand((1024, 1024), generator=g)
@@ -277,7 +284,7 @@ def run_extras(device, peaks, flush):
                                              'gflops': round(2.0 * 1024 * 64 * nnz / ms / 1e6, 1)}
     except Exception as e:
         extras['linear_fp32_1024_8x8_90'] = {'error': repr(e)[:200]}
-    return extras
+    return {k: v for k, v in extras.items() if 'skipped' not in str(v.get('error', ''))}
 
 
 def cpu_baseline_linear(x, w, b, repeats=3):
@@ -310,6 +317,8 @@ def main():
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-extras', action='store_true')
+    ap.add_argument('--extras', default=None,
+                    help='comma list of extra measurements to run: linear,attention,convert,readme (default all)')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
 
@@ -408,7 +417,8 @@ def main():
             out['cpu_baseline'] = {'value': wl['flops'] / secs / 1e12, 'unit': 'TFLOP/s', 'cores': cores,
                                    'kind': 'port', 'sample': 'whole workload, best of 3: F.linear(x, W*mask, b) fp32'}
             if not args.no_extras:
-                out['extras'] = run_extras(device, peaks, flush)
+                only = set(args.extras.split(',')) if args.extras else None
+                out['extras'] = run_extras(device, peaks, flush, only)
         print(json.dumps(out))
     if world > 1:
         import torch.distributed as dist

@@ -230,7 +230,8 @@ class BCSFunctionContext(TeSAFunctionContext):
             mask = mask.to(torch.uint8)
         if mask.dtype != torch.uint8:
             mask = (mask != 0).to(torch.uint8)
-        mask = mask.contiguous()
+        if not mask.is_contiguous():
+            mask = mask.contiguous()
         assert mask.dim() in (2, 3), 'expected a [H, W] or [n, H, W] mask'
         n = mask.shape[0] if mask.dim() == 3 else 1
         H, W = mask.shape[-2:]
@@ -240,23 +241,35 @@ class BCSFunctionContext(TeSAFunctionContext):
         cap = R * C if capacity is None else int(capacity)
         dev = mask.device
         lead = (n,) if mask.dim() == 3 else ()
-        i32 = dict(dtype=torch.int32, device=dev)
-        row_ptr = torch.empty(lead + (R + 1,), **i32) if self._BCSR else None
-        bcsr = torch.empty(lead + (cap,), **i32) if self._BCSR else None
-        col_ptr = torch.empty(lead + (C + 1,), **i32) if self._BCSC else None
+        # one int32 allocation carries every 32-bit output (host-side cost matters: the kernel itself
+        # takes tens of microseconds)
+        both = self._BCSR and self._BCSC
+        sizes = [n * (R + 1) if self._BCSR else 0, n * cap if self._BCSR else 0,
+                 n * (C + 1) if self._BCSC else 0, n * cap if (self._BCSC and not both) else 0, 2 * n]
+        # keep every piece 16-byte aligned
+        offs, total = [], 0
+        for sz in sizes:
+            offs.append(total)
+            total += (sz + 3) // 4 * 4
+        pool = torch.empty(total, dtype=torch.int32, device=dev)
+        piece = lambda i, shape: pool[offs[i]:offs[i] + sizes[i]].view(shape)
+        row_ptr = piece(0, lead + (R + 1,)) if self._BCSR else None
+        bcsr = piece(1, lead + (cap,)) if self._BCSR else None
+        col_ptr = piece(2, lead + (C + 1,)) if self._BCSC else None
         bcsc = None
         if self._BCSC:
-            bcsc = torch.empty(lead + (cap,), dtype=torch.int64 if self._BCSR else torch.int32, device=dev)
-        counts = torch.empty((2, n), **i32)  # row 0: nnz, row 1: uniform flag
+            bcsc = torch.empty(lead + (cap,), dtype=torch.int64, device=dev) if both else piece(3, lead + (cap,))
+        counts = piece(4, (2, n))  # row 0: nnz, row 1: uniform flag
         L = _lib.lib()
         ws_bytes = L.sparta_bcs_build_workspace_bytes(n, H, W, BH, BW)
         ws = _workspace(dev, ws_bytes)
-        with torch.cuda.device(dev):
-            _lib.check(L.sparta_bcs_build(
-                mask.data_ptr(), n, H, W, BH, BW, int(self._BCSR), int(self._BCSC),
-                _lib.ptr(row_ptr), _lib.ptr(bcsr), _lib.ptr(col_ptr), _lib.ptr(bcsc), cap,
-                counts[0].data_ptr(), counts[1].data_ptr(), None,
-                ws.data_ptr(), ws_bytes, _lib.stream_ptr(dev)), 'sparta_bcs_build')
+        if torch.cuda.current_device() != dev.index:
+            torch.cuda.set_device(dev)
+        _lib.check(L.sparta_bcs_build(
+            mask.data_ptr(), n, H, W, BH, BW, int(self._BCSR), int(self._BCSC),
+            _lib.ptr(row_ptr), _lib.ptr(bcsr), _lib.ptr(col_ptr), _lib.ptr(bcsc), cap,
+            counts[0].data_ptr(), counts[1].data_ptr(), None,
+            ws.data_ptr(), ws_bytes, _lib.stream_ptr(dev)), 'sparta_bcs_build')
         if self._BCSR and self._BCSC:
             return BCSRCIndexes(self, mask, row_ptr, col_ptr, bcsr, bcsc, BH, BW, cap, counts[0], counts[1])
         if self._BCSR:
