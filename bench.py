@@ -31,6 +31,9 @@ if ROOT not in sys.path:
 
 TOKENS, IN_F, OUT_F, BLOCK = 4096, 4096, 4096, 32
 SPARSITY = 0.75
+# dram__bytes_read.sum + dram__bytes_write.sum of one bsmm_dsd_tc_kernel launch on this workload
+# (profiles/bsmm_dsd_tc_linear4096_sp75.md); algorithmic bytes are 75.5 MB
+DSD75_TRAFFIC_BYTES = 44.03e6
 
 
 def load_peaks():
@@ -240,11 +243,28 @@ def run_extras(device, peaks, flush, only=None):
         fnc = sparta.tesa.get_bcs_function(32, 32, True, False)
         # the 134 MB input is larger than the 126 MB L2, so no flush is interposed here (a flush leaves
         # 126 MB of dirty lines whose write-back would be charged to this read-only kernel)
-        ms = timed(lambda: fnc.build_indexes(masks), steps=20, do_flush=False)
+        ms_api = timed(lambda: fnc.build_indexes(masks), steps=20, do_flush=False)
+        # the same conversion through the C ABI with caller-owned outputs (no per-call allocation)
+        from sparta_b200 import _lib
+        L = _lib.lib()
+        i32 = dict(dtype=torch.int32, device=device)
+        row_ptr, idxb, cnt = torch.empty((32, 65), **i32), torch.empty((32, 4096), **i32), torch.empty((2, 32), **i32)
+        nb = L.sparta_bcs_build_workspace_bytes(32, 2048, 2048, 32, 32)
+        ws = torch.zeros(nb, dtype=torch.uint8, device=device)
+        ptrs = (masks.data_ptr(), row_ptr.data_ptr(), idxb.data_ptr(), cnt[0].data_ptr(), cnt[1].data_ptr(), ws.data_ptr())
+        stream = _lib.stream_ptr(device)
+
+        def convert_cabi():
+            _lib.check(L.sparta_bcs_build(ptrs[0], 32, 2048, 2048, 32, 32, 1, 0, ptrs[1], ptrs[2], None, None, 4096,
+                                          ptrs[3], ptrs[4], None, ptrs[5], nb, stream), 'sparta_bcs_build')
+        ms = timed(convert_cabi, steps=20, do_flush=False)
         gbs = masks.numel() / ms / 1e6
         extras['bcsr_convert_32x2048x2048'] = {'us': round(ms * 1e3, 2), 'gbs': round(gbs, 1),
                                                'frac_hbm_peak': round(gbs / peaks['hbm_gbs'], 4),
-                                               'l2': 'input (134 MB) larger than L2, no flush'}
+                                               'us_python_api': round(ms_api * 1e3, 2),
+                                               'l2': 'input (134 MB) larger than L2, no flush',
+                                               'note': 'us: sparta_bcs_build through the C ABI with caller-owned '
+                                                       'outputs; us_python_api: build_indexes() incl. allocations'}
         # dynamic sparsity: conversion + dds matmul, A[32,2048,128] . B[32,128,2048]
         g = torch.Generator().manual_seed(8)
         A = torch.randn((32, 2048, 128), generator=g).half().to(device)
@@ -404,7 +424,8 @@ def main():
             'vs_baseline': None, 'dtype': 'f16 (fp32 accumulate)', 'data': 'synthetic',
             'config': config_dict(world), 'nnz_blocks': wl['nnz'],
             'roofline': {'bound': 'tensor', 'achieved': kernel_tflops, 'peak': peaks['tflops'], 'unit': 'TFLOP/s',
-                         'frac': kernel_tflops / peaks['tflops'], 'traffic': None,
+                         'frac': kernel_tflops / peaks['tflops'], 'traffic': DSD75_TRAFFIC_BYTES,
+                         'traffic_note': 'dram read+write per launch from the ncu capture in profiles/ (output stays in L2)',
                          'peak_source': f"{peaks['source']} bf16 burst", 'hbm_gbs': wl['bytes'] / ms_per_step / 1e6,
                          'hbm_frac': wl['bytes'] / ms_per_step / 1e6 / peaks['hbm_gbs']},
             'e2e': {'value': e2e_value, 'unit': 'TFLOP/s', 'ms_per_step': e2e_ms / args.steps,

@@ -9,6 +9,7 @@
 // Replaces bcs_index_1 / bcs_index_2 + torch.cumsum + .item()
 // (sparta/tesa/templates/block_compressed.cu.j2:67-170, sparta/tesa/block_compressed.py:242-309).
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace sparta {
 namespace {
@@ -33,6 +34,8 @@ struct BcsParams {
   int seg_w;           // bytes of one mask row a warp covers per unit
   int segs;            // units per block row
   int units_per_mask;
+  int bw_shift;        // log2(BW)
+  int32_t* status;     // device status words (TMA path: a bounded wait that ran out sets word 0)
 };
 
 // 0x80 in every byte of w that is zero
@@ -40,17 +43,18 @@ __device__ __forceinline__ uint32_t zero_bytes(uint32_t w) {
   return (w - 0x01010101u) & ~w & 0x80808080u;
 }
 
-// In-place inclusive scan of p[1..n] (p[0] must be 0) by one CTA of kThreads threads.
+// In-place inclusive scan of p[1..n] (p[0] must be 0) by one CTA (any power-of-two size up to 256 threads).
 __device__ void block_scan_inplace(int32_t* p, int n, int32_t* s_part) {
   const int tid = threadIdx.x;
-  const int chunk = (n + kThreads - 1) / kThreads;
+  const int nt = blockDim.x;
+  const int chunk = (n + nt - 1) / nt;
   const int lo = min(n, tid * chunk), hi = min(n, lo + chunk);
   int sum = 0;
   for (int i = lo; i < hi; ++i) sum += p[i + 1];
   s_part[tid] = sum;
   __syncthreads();
   // Hillis-Steele over 256 partials
-  for (int off = 1; off < kThreads; off <<= 1) {
+  for (int off = 1; off < nt; off <<= 1) {
     int v = tid >= off ? s_part[tid - off] : 0;
     __syncthreads();
     s_part[tid] += v;
@@ -72,7 +76,7 @@ constexpr int kPtrSmem = 2048;   // block rows / columns whose pointer array fit
 template <bool SMEM>
 __device__ void phase2(const BcsParams& p, int b, const uint8_t* occ, int32_t* s_ptr, int32_t* s_part,
                        int* s_nonuniform) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const int R = p.R, Cn = p.Cn;
   auto occ_at = [&](size_t i) -> int { return SMEM ? occ[i] : __ldcg(&occ[i]); };
   int32_t* rank = p.rank ? p.rank + (size_t)b * R * Cn : nullptr;
@@ -82,7 +86,7 @@ __device__ void phase2(const BcsParams& p, int b, const uint8_t* occ, int32_t* s
     int32_t* row_ptr = SMEM ? s_ptr : g_row_ptr;
     int32_t* out = p.bcsr_idx + (size_t)b * p.idx_capacity;
     if (threadIdx.x == 0) row_ptr[0] = 0;
-    for (int r = warp; r < R; r += kWarps) {
+    for (int r = warp; r < R; r += nwarp) {
       int cnt = 0;
       for (int c = lane; c < Cn; c += 32) {
         const int o = occ_at((size_t)r * Cn + c);
@@ -95,8 +99,8 @@ __device__ void phase2(const BcsParams& p, int b, const uint8_t* occ, int32_t* s
     __syncthreads();
     block_scan_inplace(row_ptr, R, s_part);
     if (SMEM)
-      for (int r = threadIdx.x; r <= R; r += kThreads) g_row_ptr[r] = row_ptr[r];
-    for (int r = warp; r < R; r += kWarps) {
+      for (int r = threadIdx.x; r <= R; r += blockDim.x) g_row_ptr[r] = row_ptr[r];
+    for (int r = warp; r < R; r += nwarp) {
       int off = row_ptr[r];
       for (int c0 = 0; c0 < Cn; c0 += 32) {
         const int c = c0 + lane;
@@ -118,7 +122,7 @@ __device__ void phase2(const BcsParams& p, int b, const uint8_t* occ, int32_t* s
     int32_t* g_col_ptr = p.col_ptr + (size_t)b * (Cn + 1);
     int32_t* col_ptr = SMEM ? s_ptr : g_col_ptr;
     if (threadIdx.x == 0) col_ptr[0] = 0;
-    for (int c = threadIdx.x; c < Cn; c += kThreads) {
+    for (int c = threadIdx.x; c < Cn; c += blockDim.x) {
       int cnt = 0;
       for (int r = 0; r < R; ++r) {
         const int o = occ_at((size_t)r * Cn + c);
@@ -130,11 +134,11 @@ __device__ void phase2(const BcsParams& p, int b, const uint8_t* occ, int32_t* s
     __syncthreads();
     block_scan_inplace(col_ptr, Cn, s_part);
     if (SMEM)
-      for (int c = threadIdx.x; c <= Cn; c += kThreads) g_col_ptr[c] = col_ptr[c];
+      for (int c = threadIdx.x; c <= Cn; c += blockDim.x) g_col_ptr[c] = col_ptr[c];
     const bool both = p.want_bcsr != 0;
     int32_t* out32 = reinterpret_cast<int32_t*>(p.bcsc_idx) + (size_t)b * p.idx_capacity;
     long long* out64 = reinterpret_cast<long long*>(p.bcsc_idx) + (size_t)b * p.idx_capacity;
-    for (int c = threadIdx.x; c < Cn; c += kThreads) {
+    for (int c = threadIdx.x; c < Cn; c += blockDim.x) {
       int pos = col_ptr[c];
       for (int r = 0; r < R; ++r) {
         if (occ_at((size_t)r * Cn + c) & 1) {
@@ -277,6 +281,158 @@ __global__ void __launch_bounds__(kThreads, 4) bcs_build_kernel(BcsParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Phase 1 through TMA.  The mask is described to the TMA unit as rows of 32-bit words, so one bulk
+// tensor copy can fetch a tile of 4 rows x 1 KB (four contiguous kilobytes of DRAM pages instead of many
+// short row pieces).  Each warp runs its own pipeline: three 4 KB shared-memory slots, each guarded by
+// its own mbarrier, so 12 KB per warp (192 KB per SM with sixteen warps) are in flight without holding
+// them in registers.  A lane owns the 16-byte chunks `lane` and `lane + 32` of the 64 chunks of a
+// kilobyte, reduces them over the rows of a block row (BH / 4 tiles), writes the occupancy bytes and
+// lets lane 0 re-arm the slot with the tile three steps ahead.  Phase 2 is shared with the load-based
+// kernel.  Used when the row pitch is a multiple of 16 bytes.
+// ---------------------------------------------------------------------------------------------------
+constexpr int kTmaThreads = 256;
+constexpr int kTmaWarps = kTmaThreads / 32;
+constexpr int kTmaSlots = 3;
+constexpr int kTileRows = 4, kTileCols = 1024;
+constexpr int kTileBytes = kTileRows * kTileCols;
+constexpr int kTmaSmem = kTmaWarps * kTmaSlots * kTileBytes + 256 + 1024;
+
+// `any` / `zer`: OR of the words / of the zero-byte flags of one 16-byte column chunk over the rows of
+// a block row; col is the chunk's first mask column.
+__device__ __forceinline__ void emit_blocks(const BcsParams& p, uint8_t* occ_row, const uint32_t (&any)[4],
+                                            const uint32_t (&zer)[4], int col, int lane) {
+  if (p.BW >= 16) {
+    uint32_t a = any[0] | any[1] | any[2] | any[3], z = zer[0] | zer[1] | zer[2] | zer[3];
+    const int g = p.BW >> 4;  // lanes per block: 1 .. 16, a power of two
+    for (int off = 1; off < g; off <<= 1) {
+      a |= __shfl_xor_sync(0xffffffffu, a, off);
+      z |= __shfl_xor_sync(0xffffffffu, z, off);
+    }
+    const int cb = col >> p.bw_shift;
+    if ((lane & (g - 1)) == 0 && cb < p.Cn) occ_row[cb] = a ? (z ? 3 : 1) : 0;
+  } else if (p.BW == 8) {
+    const int cb = col >> 3;
+    if (cb < p.Cn) occ_row[cb] = (any[0] | any[1]) ? ((zer[0] | zer[1]) ? 3 : 1) : 0;
+    if (cb + 1 < p.Cn) occ_row[cb + 1] = (any[2] | any[3]) ? ((zer[2] | zer[3]) ? 3 : 1) : 0;
+  } else {
+    const int cb = col >> 2;
+#pragma unroll
+    for (int w = 0; w < 4; ++w)
+      if (cb + w < p.Cn) occ_row[cb + w] = any[w] ? (zer[w] ? 3 : 1) : 0;
+  }
+}
+
+__global__ void __launch_bounds__(kTmaThreads, 2)
+bcs_build_tma_kernel(const __grid_constant__ CUtensorMap tm, BcsParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kTmaWarps * kTmaSlots * kTileBytes);
+  const int b = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint8_t* occ = p.occ + (size_t)b * p.R * p.Cn;
+  uint8_t* ring = smem + warp * kTmaSlots * kTileBytes;
+  uint64_t* bar = bars + warp * kTmaSlots;
+
+  // a unit = one block row (BH rows) x 1024 columns = BH / 4 tiles
+  const int tiles_per_unit = p.BH / kTileRows;
+  const int segs = (p.W + kTileCols - 1) / kTileCols;
+  const int units = p.R * segs;
+  // each warp takes a contiguous run of units
+  const int wid = blockIdx.x * kTmaWarps + warp, nw = gridDim.x * kTmaWarps;
+  const int u0 = (int)((long long)units * wid / nw);
+  const int n_units = (int)((long long)units * (wid + 1) / nw) - u0;
+  const int n_tiles = n_units * tiles_per_unit;
+
+  if (lane == 0) {
+    for (int s = 0; s < kTmaSlots; ++s) tc::mbar_init(&bar[s], 1);
+    tc::fence_mbar_init();
+  }
+  __syncwarp();
+  // cursors over (block row, segment, tile of the unit), advanced without divisions: one for the
+  // producer lane (three tiles ahead) and one for the consumer
+  struct Cursor { int br, sg, sub; };
+  auto advance = [&](Cursor& c) {
+    if (++c.sub == tiles_per_unit) {
+      c.sub = 0;
+      if (++c.sg == segs) { c.sg = 0; ++c.br; }
+    }
+  };
+  Cursor pc = {u0 / segs, u0 % segs, 0}, cc = pc;
+  int ps = 0;  // slot the producer fills next
+  auto issue = [&]() {
+    tc::mbar_arrive_expect_tx(&bar[ps], kTileBytes);
+    // x in 32-bit words: a multiple of 256 words, so the copy starts on a 1 KB boundary of the row
+    tc::tma_load_2d(ring + ps * kTileBytes, &tm, pc.sg * (kTileCols / 4), b * p.H + pc.br * p.BH + pc.sub * kTileRows,
+                    &bar[ps]);
+    advance(pc);
+    ps = (ps == kTmaSlots - 1) ? 0 : ps + 1;
+  };
+  if (lane == 0)
+    for (int t = 0; t < min(kTmaSlots, n_tiles); ++t) issue();
+
+  uint32_t any0[4] = {0, 0, 0, 0}, zer0[4] = {0, 0, 0, 0}, any1[4] = {0, 0, 0, 0}, zer1[4] = {0, 0, 0, 0};
+  int s = 0;
+  uint32_t parity = 0;
+  for (int t = 0; t < n_tiles; ++t) {
+    if (!tc::mbar_wait(&bar[s], parity)) {
+      if (lane == 0 && p.status) atomicExch(&p.status[0], 1);
+      break;
+    }
+    const uint4* tile = reinterpret_cast<const uint4*>(ring + s * kTileBytes);
+#pragma unroll
+    for (int r = 0; r < kTileRows; ++r) {
+      const uint4 v = tile[r * 64 + lane], w = tile[r * 64 + 32 + lane];
+      any0[0] |= v.x; any0[1] |= v.y; any0[2] |= v.z; any0[3] |= v.w;
+      zer0[0] |= zero_bytes(v.x); zer0[1] |= zero_bytes(v.y); zer0[2] |= zero_bytes(v.z); zer0[3] |= zero_bytes(v.w);
+      any1[0] |= w.x; any1[1] |= w.y; any1[2] |= w.z; any1[3] |= w.w;
+      zer1[0] |= zero_bytes(w.x); zer1[1] |= zero_bytes(w.y); zer1[2] |= zero_bytes(w.z); zer1[3] |= zero_bytes(w.w);
+    }
+    __syncwarp();  // every lane has read the slot before it is re-armed
+    if (lane == 0 && t + kTmaSlots < n_tiles) issue();
+    if (cc.sub == tiles_per_unit - 1) {
+      uint8_t* occ_row = occ + (size_t)cc.br * p.Cn;
+      const int col = cc.sg * kTileCols + lane * 16;
+      emit_blocks(p, occ_row, any0, zer0, col, lane);
+      emit_blocks(p, occ_row, any1, zer1, col + 512, lane);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) any0[i] = zer0[i] = any1[i] = zer1[i] = 0;
+    }
+    advance(cc);
+    if (++s == kTmaSlots) { s = 0; parity ^= 1; }
+  }
+
+  // ---------------- ticket + phase 2 (as in the load-based kernel) ----------------
+  __shared__ int s_last;
+  __shared__ int32_t s_part[256];
+  __shared__ int s_nonuniform;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned ticket = atomicAdd(&p.counters[b], 1u);
+    s_last = (ticket == gridDim.x - 1);
+    s_nonuniform = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // the tile ring is idle now: reuse it for the occupancy bytes and the pointer array
+  uint8_t* s_occ = smem;
+  int32_t* s_ptr = reinterpret_cast<int32_t*>(smem + kOccSmem);
+  const int R = p.R, Cn = p.Cn;
+  const bool fast = (size_t)R * Cn <= kOccSmem && R <= kPtrSmem && Cn <= kPtrSmem &&
+                    (((size_t)b * R * Cn) % 16 == 0);
+  if (fast) {
+    const int n16 = (R * Cn + 15) / 16;
+    for (int i = threadIdx.x; i < n16; i += blockDim.x)
+      reinterpret_cast<uint4*>(s_occ)[i] = __ldcg(reinterpret_cast<const uint4*>(occ) + i);
+    __syncthreads();
+    phase2<true>(p, b, s_occ, s_ptr, s_part, &s_nonuniform);
+  } else {
+    phase2<false>(p, b, occ, nullptr, s_part, &s_nonuniform);
+  }
+}
+
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace
@@ -317,6 +473,7 @@ extern "C" int sparta_bcs_build(const uint8_t* mask, int n_masks, int H, int W, 
   p.row_ptr = row_ptr; p.bcsr_idx = bcsr_idx; p.col_ptr = col_ptr; p.bcsc_idx = bcsc_idx;
   p.idx_capacity = idx_capacity;
   p.nnz = nnz; p.uniform = uniform;
+  p.status = nullptr;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.occ = ws;
   p.rank = (want_bcsr && want_bcsc) ? reinterpret_cast<int32_t*>(ws + align_up(blocks, 256)) : nullptr;
@@ -327,6 +484,8 @@ extern "C" int sparta_bcs_build(const uint8_t* mask, int n_masks, int H, int W, 
   p.seg_w = (32 * vw > BW) ? 32 * vw : BW;
   p.segs = (W + p.seg_w - 1) / p.seg_w;
   p.units_per_mask = R * p.segs;
+  p.bw_shift = 0;
+  while ((1 << p.bw_shift) < BW) ++p.bw_shift;
 
   // spread the units of all masks over the warps resident at once (148 SMs x 4 CTAs x 8 warps), so
   // the grid is a single wave
@@ -337,10 +496,38 @@ extern "C" int sparta_bcs_build(const uint8_t* mask, int n_masks, int H, int W, 
   if (ctas < 1) ctas = 1;
   dim3 grid(ctas, n_masks), block(kThreads);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (vec16)
-    bcs_build_kernel<16><<<grid, block, 0, st>>>(p);
-  else
-    bcs_build_kernel<4><<<grid, block, 0, st>>>(p);
+  bool launched = false;
+  if (vec16 && (long long)n_masks * H <= 0x7fffffffll && tc::encode_tiled_fn() != nullptr) {
+    // TMA streaming path: two CTAs of eight warps per SM, every warp with its own three-slot pipeline
+    CUtensorMap tm;
+    const uint64_t dims[2] = {(uint64_t)W / 4, (uint64_t)n_masks * H};  // rows of 32-bit words
+    const uint64_t strides[1] = {(uint64_t)W};
+    const uint32_t box[2] = {kTileCols / 4, kTileRows};
+    if (tc::make_tensor_map(&tm, mask, tc::kTensorMapU32, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE) ==
+        SPARTA_OK) {
+      static bool attr_set = false;
+      if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(bcs_build_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kTmaSmem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        attr_set = true;
+      }
+      const int units = R * ((W + kTileCols - 1) / kTileCols);
+      int per_mask = (2 * kNumSMs) / n_masks;                       // fill the 296 CTA slots once
+      const int by_units = (units + kTmaWarps - 1) / kTmaWarps;     // at least one unit per warp
+      if (per_mask > by_units) per_mask = by_units;
+      if (per_mask < 1) per_mask = 1;
+      p.status = tc::device_status_ptr();
+      bcs_build_tma_kernel<<<dim3(per_mask, n_masks), kTmaThreads, kTmaSmem, st>>>(tm, p);
+      launched = true;
+    }
+  }
+  if (!launched) {
+    if (vec16)
+      bcs_build_kernel<16><<<grid, block, 0, st>>>(p);
+    else
+      bcs_build_kernel<4><<<grid, block, 0, st>>>(p);
+  }
   int rc = launch_status();
   if (rc != SPARTA_OK) return rc;
   if (h_nnz) {

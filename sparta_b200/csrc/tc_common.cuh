@@ -222,7 +222,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 // cuTensorMapEncodeTiled through the runtime's driver-entry-point lookup; nullptr when unavailable.
 EncodeTiledFn encode_tiled_fn();
 
-// rank-2 or rank-3 row-major tensor of 2-byte elements; dims / box listed innermost first.
+constexpr int kTensorMapU8 = 100;   // dtype code for byte tensors (masks); SPARTA_F16 / SPARTA_BF16 otherwise
+constexpr int kTensorMapU32 = 101;  // bytes viewed as 32-bit words, which allows boxes up to 1 KB wide
+
+// rank-2 or rank-3 row-major tensor of 2-byte (or, with kTensorMapU8 / kTensorMapU32, 1- / 4-byte) elements; dims / box listed innermost first.
 // Returns a status code of sparta_b200.h.
 int make_tensor_map(CUtensorMap* map, const void* base, int dtype, int rank, const uint64_t* dims,
                     const uint64_t* strides_bytes /* rank-1 entries */, const uint32_t* box,
