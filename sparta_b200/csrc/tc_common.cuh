@@ -52,14 +52,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait that lets the hardware suspend the warp for up to `hint_ns` until the phase completes: a
+// waiting warp then issues almost nothing, instead of flooding the memory-instruction queue that TMA
+// issue, shared-memory loads and tcgen05 traffic of the working warps also go through.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: false when the phase did not complete within kWaitNanos.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   while (true) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
+    for (int i = 0; i < 16; ++i)
+      if (mbar_try_wait_suspend(bar, parity, 4000u)) return true; else __nanosleep(100);
     if (global_timer_ns() - t0 > kWaitNanos) return false;
   }
 }
