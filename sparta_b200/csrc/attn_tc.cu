@@ -139,6 +139,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const long long q_row0 = (long long)head * p.Nt + (long long)tile * kTileM;
   const long long kv_row0 = (long long)head * p.Ns;
 
+  bool failed = false;  // a bounded wait of this thread gave up
   if (warp == 4) {
     // ------------------------------ producer ------------------------------
     if (lane == 0 && count > 0) {
@@ -166,6 +167,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                         (int)(kv_row0 + (long long)kb * kBlk), &v_full[vs]);
         }
       }
+      failed |= !ok;
       if (!ok) atomicExch(&p.status[0], 1);
     }
   } else if (warp == 5) {
@@ -192,6 +194,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
       __syncwarp();
     }
+    failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[1], 1);
   } else if (warp == 6) {
     // ------------------------------ O += P V ------------------------------
@@ -220,6 +223,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
       __syncwarp();
     }
+    failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[2], 1);
   } else {
     // ------------------------------ softmax + epilogue (warps 0-3) ------------------------------
@@ -236,7 +240,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const bool have0 = (e0 >> half) & 1, have1 = (e1 >> half) & 1;
       const int kb[2] = {e0 >> 2, e1 >> 2};
       const bool have[2] = {have0, have1};
-      if (!mbar_wait(&s_full[sb], (j / kSBuf) & 1)) { ok = false; break; }
+      if (!mbar_wait_warp(&s_full[sb], (j / kSBuf) & 1)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t s_addr = tmem_base + lane_base + sb * kPair;
       // ---- pass 1: row maximum over the kept, unmasked scores ----
@@ -271,7 +275,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         l_run *= alpha;
       }
       // previous P V must be finished before P is overwritten or O is rescaled
-      if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
+      if (j > 0 && !mbar_wait_warp(pv_done, (j - 1) & 1)) { ok = false; break; }
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
         tc_fence_after_sync();
 #pragma unroll
@@ -350,7 +354,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
     }
     // ---- epilogue: O / l -> global ----
-    if (ok && npairs > 0 && !mbar_wait(pv_done, (npairs - 1) & 1)) ok = false;
+    if (ok && npairs > 0 && !mbar_wait_warp(pv_done, (npairs - 1) & 1)) ok = false;
+    failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[3], 1);
     tc_fence_after_sync();
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -388,7 +393,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  sync_and_drain(failed);
   if (warp == 5) {
     tc_fence_after_sync();
     tmem_dealloc<C::kTmemCols>(tmem_base);

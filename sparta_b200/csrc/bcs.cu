@@ -374,9 +374,11 @@ bcs_build_tma_kernel(const __grid_constant__ CUtensorMap tm, BcsParams p) {
   uint32_t any0[4] = {0, 0, 0, 0}, zer0[4] = {0, 0, 0, 0}, any1[4] = {0, 0, 0, 0}, zer1[4] = {0, 0, 0, 0};
   int s = 0;
   uint32_t parity = 0;
+  bool failed = false;  // a bounded wait gave up: tiles of this warp may still be in flight
   for (int t = 0; t < n_tiles; ++t) {
-    if (!tc::mbar_wait(&bar[s], parity)) {
+    if (!tc::mbar_wait_warp(&bar[s], parity)) {
       if (lane == 0 && p.status) atomicExch(&p.status[0], 1);
+      failed = true;
       break;
     }
     const uint4* tile = reinterpret_cast<const uint4*>(ring + s * kTileBytes);
@@ -406,7 +408,7 @@ bcs_build_tma_kernel(const __grid_constant__ CUtensorMap tm, BcsParams p) {
   __shared__ int s_last;
   __shared__ int32_t s_part[256];
   __shared__ int s_nonuniform;
-  __syncthreads();
+  tc::sync_and_drain(failed);
   if (threadIdx.x == 0) {
     __threadfence();
     const unsigned ticket = atomicAdd(&p.counters[b], 1u);

@@ -1,8 +1,6 @@
 // Internal parameter block shared by the block-sparse matmul kernels.
 #pragma once
 
-#include <cstdlib>
-
 #include "common.cuh"
 
 namespace sparta {
@@ -32,16 +30,11 @@ int bsmm_simt(const BsmmParams& p, cudaStream_t st);
 // tcgen05 kernels: return SPARTA_ERR_UNSUPPORTED when the configuration is outside their coverage.
 bool dsd_tc_supported(const BsmmParams& p);
 int dsd_tc_launch(const BsmmParams& p, cudaStream_t st);
-bool dsd_ts_supported(const BsmmParams& p);
-int dsd_ts_launch(const BsmmParams& p, cudaStream_t st);
 bool dds_tc_supported(const BsmmParams& p);
 int dds_tc_launch(const BsmmParams& p, cudaStream_t st);
 inline bool bsmm_tc_supported(const BsmmParams& p) { return dsd_tc_supported(p) || dds_tc_supported(p); }
 inline int bsmm_tc(const BsmmParams& p, cudaStream_t st) {
-  if (p.mode == MODE_DDS) return dds_tc_launch(p, st);
-  const char* e = getenv("SPARTA_DSD_IMPL");
-  if (e && e[0] == 't') return dsd_ts_launch(p, st);  // work in progress: activations through tensor memory
-  return dsd_tc_launch(p, st);
+  return p.mode == MODE_DDS ? dds_tc_launch(p, st) : dsd_tc_launch(p, st);
 }
 
 // whether the tcgen05 matmul / fused attention kernels are compiled into this build

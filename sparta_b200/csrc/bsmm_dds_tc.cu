@@ -129,6 +129,7 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   const uint32_t tmem_base = *tmem_holder;
   const int nchunks = p.K / kChunkK;
 
+  bool failed = false;  // a bounded wait of this thread gave up
   if (warp == 4) {
     // ------------------------------ producer ------------------------------
     const int col = lane < ncols ? clist[c_first + lane] : 0;
@@ -147,6 +148,7 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         else tma_load_2d(dst, &tm_b, col * kBlk, batch * p.K + c * kChunkK, &full_bar[s]);
       }
     }
+    failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[0], 1);
   } else if (warp == 5) {
     // ------------------------------ MMA issue ------------------------------
@@ -173,11 +175,13 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       }
       __syncwarp();
     }
+    failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[1], 1);
     if (lane == 0) umma_commit(accum_bar);
   } else {
     // ------------------------------ epilogue: kept blocks only ------------------------------
-    if (!mbar_wait(accum_bar, 0)) {
+    if (!mbar_wait_warp(accum_bar, 0)) {
+      failed = true;
       if (lane == 0) atomicExch(&p.status[2], 1);
     } else {
       tc_fence_after_sync();
@@ -219,7 +223,7 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  sync_and_drain(failed);
   if (warp == 5) {
     tc_fence_after_sync();
     tmem_dealloc<256>(tmem_base);

@@ -1,0 +1,467 @@
+// Block-sparse matmul on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), fp16 / bf16.
+//
+// dsd, B stored [N, K] as BCSR 32 x 32 blocks (the SparseLinear weight layout):
+//   C[m, n] = sum over kept K-blocks k of row-block n:  X[m, k-block] . W_block(n, k)^T   (+ bias)
+//
+// Why the activations go through tensor memory.  With both operands in shared memory a
+// tcgen05.mma M128 N32 K16 reads 4 KB of A and 1 KB of B; at 128 B per cycle that is 40 cycles for
+// 16 cycles of math, so 32-wide blocks cannot pass 40 % of the tensor peak however they are issued.
+// With A in tensor memory only the 1 KB of B crosses the shared-memory port and the same instruction
+// runs at its 16-cycle rate (measured: four issuing threads, 16.2 cycles per MMA).  The activations of
+// a K-block are shared by every W block of that K-block in the CTA's panel, so they are moved into
+// tensor memory once per K-block and reused from there.
+//
+// One CTA owns 128 token rows x a panel of NP = 12 block columns, i.e. 12 fp32 accumulators of
+// 128 x 32 in tensor memory (384 columns), plus a ring of kASlots = 4 activation tiles (128 lanes x 32
+// columns each) in the remaining 128 columns.  The shared-memory rings that TMA fills run deeper
+// (kXSlots = 6 steps), because a step's loads take far longer to arrive than its MMAs take to run.
+// A "step" is an aligned pair of K-blocks (64 values of K) of which at least one is kept by a
+// row-block of the panel: 128-byte rows are the widest a swizzled TMA box can fetch, and a bulk tensor
+// load costs the TMA unit about 1.3-1.9 cycles per box row however wide the row is, so fetching the
+// activations in 64-byte rows would cost twice as much per K-block.  The prologue turns the BCSR
+// rows of the panel into a complete schedule in shared memory -- per step its K-block, the W blocks
+// it needs (kmask of its two K-blocks), where each of them sits in the value array (wsrc), its position in the W ring
+// (cum_w) and the earlier step whose release makes room for it (wait_for) -- so the roles below run
+// without per-step messages and with almost no bookkeeping of their own; a single warp executes
+// dependent instructions at only one per ~5 cycles, which made run-time bookkeeping the bottleneck.
+//   warps 4-7    producers: warp j issues the TMA loads of steps j, j + 4, ... (X tile by coordinate,
+//                W blocks gathered by BCSR position, one per lane in a single instruction; all complete
+//                on the step's "full" mbarrier).  Issuing one bulk tensor load costs the issuing warp
+//                50-140 cycles, hence four warps.
+//   warps 0-3,   converters: shared memory -> registers -> tcgen05.st into the step's slot of the
+//   12-15        activation ring (each warp its own 32-lane quadrant; the two sets alternate steps),
+//                then arrive on the step's "a_full" mbarrier
+//   warps 8-11   MMA issue: each warp owns the accumulators l with l % 4 == its index and one of its
+//                threads issues tcgen05.mma with A from tensor memory (two K = 16 slabs per W block).
+//                A wait, a commit and an MMA each cost the issuing thread 80-100 cycles, which is why
+//                a step spans two K-blocks and why every issuer thread counts;
+//                tcgen05.commit arrives on the step's "empty" mbarrier, which frees the X tile, the W
+//                blocks and the activation slot once all four have arrived.  One thread sustains about
+//                one MMA per 45 cycles, hence four issuers.
+//   warps 0-3, 12-15 afterwards: epilogue, tcgen05.ld -> + bias -> fp16 / bf16 -> global
+// Every mbarrier wait is bounded; a wait that runs out sets a status word and the CTA winds down.
+//
+// Replaces sparta_sparse_matmul_dsd.cuh.j2 / openai_sparse_matmul_dsd.cuh.j2 for this layout.
+#include <type_traits>
+
+#include "bsmm.cuh"
+#include "tc_common.cuh"
+
+namespace sparta {
+namespace {
+
+using namespace tc;
+
+constexpr int kBlk = 32;            // BCSR block edge (K and N)
+constexpr int kTileM = 128;         // token rows per CTA
+constexpr int kStepK = 2 * kBlk;    // K values per step: an aligned pair of K-blocks
+constexpr int kXBytes = kTileM * kStepK * 2;  // 16 KB: 128 rows x 128 B
+constexpr int kWBytes = kBlk * kBlk * 2;      // 2 KB
+constexpr int kACols = kStepK / 2;  // tensor-memory columns of one activation tile (two 16-bit values per column)
+constexpr int kNP = 12;             // block columns per CTA
+constexpr int kMaxKb = 1024;        // K-blocks the schedule can hold (K <= 32768)
+constexpr int kMaxSteps = kMaxKb / 2;
+constexpr int kXSlots = 6;          // steps whose loads (X tile, W blocks) are in flight
+constexpr int kASlots = 4;          // steps whose activations sit in tensor memory; a power of two
+constexpr int kWSlots = 40;         // W blocks in flight
+constexpr int kMmaWarps = 12;       // MMA-issuing warps: one per accumulator
+constexpr int kConvSets = 2;        // converter warp sets (four warps each) that alternate steps
+constexpr int kProdWarps = 4;       // TMA-issuing warps; at most kXSlots (see the producers' wait)
+constexpr int kProd0 = 4;           // first producer warp
+constexpr int kMma0 = kProd0 + kProdWarps;   // first MMA-issuing warp
+constexpr int kConv1 = kMma0 + kMmaWarps;    // first warp of the second converter set (a multiple of 4)
+constexpr int kThreads = 32 * (kConv1 + 4);  // 768
+static_assert(kProdWarps <= kXSlots && kASlots <= kXSlots, "a producer may run at most one ring turn ahead of the release it waits for");
+static_assert(kConv1 % 4 == 0, "converter warps must map onto their tensor-memory lane quadrant");
+static_assert(kNP <= 12 && kNP % kMmaWarps == 0, "a step record packs two 12-bit block masks");
+static_assert(kWSlots >= 2 * kNP && kWSlots < 64, "a step's W blocks must fit the ring; its position packs into 6 bits");
+
+struct DsdTcParams {
+  const int32_t* row_ptr;
+  const int32_t* idx;
+  const void* bias;
+  void* C;
+  int M, N, Kb, Nb;
+  long long val_stride_blocks;
+  int32_t* status;
+};
+
+constexpr uint32_t kAccCols = kNP * kBlk;   // 384
+constexpr uint32_t kTmemCols = 512;
+static_assert(kAccCols + kASlots * kACols <= kTmemCols, "tensor memory budget");
+
+// shared-memory carve-up (byte offsets from a 1 KB aligned base)
+constexpr int kOffX = 0;                                  // X ring   [kXSlots][128 rows x 128 B]
+constexpr int kOffW = kOffX + kXSlots * kXBytes;           // W ring   [kWSlots][2 KB]
+constexpr int kOffMask = kOffW + kWSlots * kWBytes;       // kmask    [Kb]        u32: row-blocks keeping K-block k
+constexpr int kOffSrc = kOffMask + kMaxKb * 4;            // wsrc     [Kb][kNP]   u16: BCSR position within the panel
+constexpr int kOffStep = kOffSrc + kMaxKb * kNP * 2;      // step_kp  [steps]     u16: K-pair index
+constexpr int kOffCum = kOffStep + kMaxSteps * 2;         // cum_w    [steps + 1] u16: W blocks of all earlier steps
+constexpr int kOffWait = kOffCum + (kMaxSteps + 8) * 2;   // wait_for [steps]     s16
+constexpr int kOffRec = kOffWait + kMaxSteps * 2;         // rec      [steps]     u32: mask0 | mask1 << 12 | ring pos << 24
+constexpr int kOffBias = kOffRec + kMaxSteps * 4;         // bias     [kNP * 32]  f32
+constexpr int kOffCtl = kOffBias + kNP * kBlk * 4;        // mbarriers and scalars
+constexpr int kSmemTotal = kOffCtl + 512 + 1024 /* alignment slack */;
+static_assert(kOffRec % 4 == 0 && kOffBias % 8 == 0 && kOffCtl % 8 == 0, "alignment of the shared-memory tables");
+
+constexpr uint32_t mine_mask(int np, int issuers) {
+  uint32_t m = 0;
+  for (int l = 0; l < np; l += issuers) m |= 1u << l;
+  return m;
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(kThreads, 1)
+bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                   DsdTcParams p) {
+  using T = typename std::conditional<FMT == 0, __half, __nv_bfloat16>::type;
+  constexpr int NP = kNP;
+  constexpr int kIssuers = kMmaWarps;
+  constexpr uint32_t kMineBase = mine_mask(NP, kMmaWarps);  // accumulators l with l % kIssuers == 0
+  constexpr uint32_t kLow = (1u << NP) - 1u;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* x_ring = smem + kOffX;
+  uint8_t* w_ring = smem + kOffW;
+  uint32_t* kmask = reinterpret_cast<uint32_t*>(smem + kOffMask);
+  uint16_t* wsrc = reinterpret_cast<uint16_t*>(smem + kOffSrc);
+  uint16_t* step_kp = reinterpret_cast<uint16_t*>(smem + kOffStep);
+  uint16_t* cum_w = reinterpret_cast<uint16_t*>(smem + kOffCum);
+  int16_t* wait_for = reinterpret_cast<int16_t*>(smem + kOffWait);
+  uint32_t* rec = reinterpret_cast<uint32_t*>(smem + kOffRec);
+  float* s_bias = reinterpret_cast<float*>(smem + kOffBias);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kOffCtl);  // [kXSlots] loads of a step have landed
+  uint64_t* empty_bar = full_bar + kXSlots;                // [kXSlots] MMAs of a step have read their operands
+  uint64_t* afull_bar = empty_bar + kXSlots;               // [kASlots] the step's activations are in tensor memory
+  uint64_t* accum_bar = afull_bar + kASlots;               // [1]       all MMAs of the tile are done
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  int* s_range = reinterpret_cast<int*>(tmem_holder + 1);  // [2] BCSR entries of the panel
+  int* s_nsteps = s_range + 2;
+  uint32_t* s_written = reinterpret_cast<uint32_t*>(s_nsteps + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int panel = blockIdx.x, m0 = blockIdx.y * kTileM, batch = blockIdx.z;
+  const int nb0 = panel * NP;
+  const int nb_end = min(nb0 + NP, p.Nb);
+  const bool is_conv = warp < 4 || warp >= kConv1;
+  const int conv_set = warp < 4 ? 0 : 1;
+  const int quad = warp & 3;  // tensor-memory lane quadrant this warp may access
+  const int n_pairs = (p.Kb + 1) / 2;
+
+  // ------------------------------ prologue: barriers, tensor memory, schedule ------------------------------
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kXSlots; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kIssuers);
+    }
+    for (int s = 0; s < kASlots; ++s) mbar_init(&afull_bar[s], 4);
+    mbar_init(accum_bar, kIssuers);
+    fence_mbar_init();
+    s_range[0] = p.row_ptr[nb0];
+    s_range[1] = p.row_ptr[nb_end];
+  }
+  if (warp == kProd0 && lane == 0) {
+    prefetch_tensormap(&tm_x);
+    prefetch_tensormap(&tm_w);
+  }
+  if (warp == kMma0) tmem_alloc<kTmemCols>(tmem_holder);
+  for (int k = threadIdx.x; k < 2 * n_pairs; k += kThreads) kmask[k] = 0;  // includes the pad block of an odd Kb
+  {
+    const T* bias = p.bias ? static_cast<const T*>(p.bias) + (long long)batch * p.N : nullptr;
+    for (int j = threadIdx.x; j < NP * kBlk; j += kThreads) {
+      const int n = nb0 * kBlk + j;
+      s_bias[j] = (bias && n < p.N) ? to_float(bias[n]) : 0.f;
+    }
+  }
+  __syncthreads();
+  // the rows of a panel are consecutive in the BCSR array: entry = (row-block << 16) | K-block
+  const int e0 = s_range[0];
+  for (int e = e0 + threadIdx.x; e < s_range[1]; e += kThreads) {
+    const int v = __ldg(p.idx + e);
+    const int k = v & 0xffff, l = (v >> 16) - nb0;
+    if (k < p.Kb && l >= 0 && l < NP) {  // index arrays come from the caller: never index shared memory with them unchecked
+      atomicOr(&kmask[k], 1u << l);
+      wsrc[k * NP + l] = static_cast<uint16_t>(e - e0);
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // compact the kept K-pairs into steps and prefix-sum their W block counts
+    int base = 0, wbase = 0;
+    uint32_t wr = 0;
+    for (int c = 0; c < n_pairs; c += 32) {
+      const int kp = c + lane;
+      const uint32_t m = kp < n_pairs ? (kmask[2 * kp] | (kmask[2 * kp + 1] << NP)) : 0u;
+      wr |= (m | (m >> NP)) & kLow;
+      const unsigned bal = __ballot_sync(0xffffffffu, m != 0u);
+      const int ord = base + __popc(bal & ((1u << lane) - 1u));
+      const int w = __popc(m);
+      int incl = w;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += t;
+      }
+      if (m) {
+        step_kp[ord] = static_cast<uint16_t>(kp);
+        cum_w[ord] = static_cast<uint16_t>(wbase + incl - w);
+      }
+      base += __popc(bal);
+      wbase += __shfl_sync(0xffffffffu, incl, 31);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wr |= __shfl_xor_sync(0xffffffffu, wr, o);
+    if (lane == 0) {
+      cum_w[base] = static_cast<uint16_t>(wbase);
+      *s_nsteps = base;
+      *s_written = wr;
+    }
+  }
+  __syncthreads();
+  const int n_steps = *s_nsteps;
+  // step s may be issued once the step that last used its X slot (s - kXSlots) and step wait_for[s], the
+  // latest one whose W blocks still occupy the ring positions s needs, have been released
+  for (int s = threadIdx.x; s < n_steps; s += kThreads) {
+    const int target = static_cast<int>(cum_w[s + 1]) - kWSlots;
+    int f = -1;
+    if (target > 0) {
+      int lo = 0, hi = s;  // cum_w[s] >= target because a step holds at most 2 NP <= kWSlots blocks
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (static_cast<int>(cum_w[mid]) >= target) hi = mid; else lo = mid + 1;
+      }
+      f = lo - 1;
+    }
+    wait_for[s] = static_cast<int16_t>(f);
+    const int kp = step_kp[s];
+    rec[s] = kmask[2 * kp] | (kmask[2 * kp + 1] << NP) | (static_cast<uint32_t>(cum_w[s] % kWSlots) << 24);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t a_tmem = tmem_base + kAccCols;  // activation ring
+
+  bool failed = false;  // a bounded wait of this thread gave up
+  if (warp >= kProd0 && warp < kMma0) {
+    // ------------------------------ producers ------------------------------
+    // lanes 0 .. NP-1 fetch the W blocks of the pair's first K-block, lanes 16 .. 16+NP-1 those of the second
+    const long long wrow0 = ((long long)batch * p.val_stride_blocks + e0) * kBlk;  // row in the [blocks * 32, 32] view
+    const int half = lane >> 4, l = lane & 15;
+    bool ok = true;
+    for (int s = warp - kProd0; s < n_steps; s += kProdWarps) {
+      const int kp = step_kp[s];
+      const uint32_t r = rec[s];
+      const uint32_t pack = (r & kLow) | (((r >> NP) & kLow) << 16);  // one bit per lane that has a block to fetch
+      const int c0 = (r >> 24) & 0x3f, wf = wait_for[s];
+      const bool have = (pack >> lane) & 1u;
+      const int src = have ? wsrc[(2 * kp + half) * NP + l] : 0;
+      // An mbarrier wait names a phase by its parity only, so a waiter must know that the barrier is
+      // at most one phase away from the one it names.  Releases are monotonic and this warp's previous
+      // step (s - kProdWarps) confirmed the release of step s - kProdWarps - kXSlots, the predecessor of
+      // step s - kXSlots on this slot's barrier: waiting for s - kXSlots is safe.  After it, everything
+      // up to s - kXSlots is known to be released, which covers the predecessor of any later step wf.
+      if (s >= kXSlots && !mbar_wait_warp(&empty_bar[s % kXSlots], ((s - kXSlots) / kXSlots) & 1)) { ok = false; break; }
+      if (wf >= 0 && wf > s - kXSlots && !mbar_wait_warp(&empty_bar[wf % kXSlots], (wf / kXSlots) & 1)) { ok = false; break; }
+      const int slot = s % kXSlots;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&full_bar[slot], kXBytes + __popc(pack) * kWBytes);
+        tma_load_2d(x_ring + slot * kXBytes, &tm_x, kp * kStepK, batch * p.M + m0, &full_bar[slot]);
+      }
+      __syncwarp();  // the expected byte count is registered before any lane's load can complete
+      if (have) {
+        int ws = c0 + __popc(pack & ((1u << lane) - 1u));  // rank among the step's blocks
+        if (ws >= kWSlots) ws -= kWSlots;
+        tma_load_2d(w_ring + ws * kWBytes, &tm_w, 0, (int)(wrow0 + (long long)src * kBlk), &full_bar[slot]);
+      }
+      __syncwarp();
+    }
+    failed |= !ok;
+    if (!ok && lane == 0) atomicExch(&p.status[0], 1);
+  } else if (warp >= kMma0 && warp < kConv1) {
+    // ------------------------------ MMA issue ------------------------------
+    // Operand addresses derive from the schedule only, so they stay warp-uniform; one lane issues.
+    constexpr uint32_t idesc = make_idesc_f16(kTileM, kBlk, FMT, 0, 0);
+    const uint32_t w_base = smem_u32(w_ring);
+    const uint64_t desc_hi = make_smem_desc(0, 16, 512, SW_64B);
+    const bool leader = lane == 0;
+    const uint32_t mine = kMineBase << (warp - kMma0);  // accumulators issued by this warp
+    uint32_t written = 0;
+    bool ok = true;
+    uint32_t r_next = n_steps > 0 ? rec[0] : 0u;
+    for (int s = 0; s < n_steps; ++s) {
+      const uint32_t r = r_next;
+      if (s + 1 < n_steps) r_next = rec[s + 1];  // fetched ahead of the wait
+      const int slot = s % kXSlots, aslot = s & (kASlots - 1);
+      // Every issuer waits for the activations of every step and commits to its "empty" barrier, also
+      // in a step in which it has no block.  The wait keeps it within one ring turn of the converters,
+      // so a phase parity is never mistaken for an older one; the commit makes the release of steps
+      // monotonic (a released step implies that every issuer's MMAs of all earlier steps are done),
+      // which is what the producers' wait_for table assumes.  The step's "full" phase completed before
+      // its converters ran, so the W blocks are in place too.
+      if (!mbar_wait(&afull_bar[aslot], (s / kASlots) & 1)) { ok = false; break; }
+      const uint32_t mk[2] = {r & kLow, (r >> NP) & kLow};
+      if (((mk[0] | mk[1]) & mine) == 0u) {
+        if (leader) umma_commit(&empty_bar[slot]);
+        continue;
+      }
+      tc_fence_after_sync();
+      const uint32_t c0 = (r >> 24) & 0x3fu;
+      const uint32_t n_first = __popc(mk[0]);  // the ring holds the first K-block's W blocks, then the second's
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        uint32_t m = mk[j] & mine;
+        const uint32_t a_addr = a_tmem + aslot * kACols + j * (kACols / 2);
+        while (m) {
+          const int l = __ffs(m) - 1;
+          m &= m - 1;
+          uint32_t w = c0 + (j ? n_first : 0u) + __popc(mk[j] & ((1u << l) - 1u));  // rank among the step's blocks
+          if (w >= kWSlots) w -= kWSlots;
+          const uint32_t b_lo = (w_base + w * kWBytes) >> 4;
+          if (leader) {
+            umma_ts(tmem_base + l * kBlk, a_addr, desc_hi | b_lo, idesc, (written >> l) & 1u);
+            umma_ts(tmem_base + l * kBlk, a_addr + kACols / 4, desc_hi | (b_lo + 2), idesc, 1u);
+          }
+          written |= 1u << l;
+        }
+      }
+      if (leader) umma_commit(&empty_bar[slot]);  // frees the step's X tile, W blocks and activation slot
+    }
+    failed |= !ok;
+    if (!ok && lane == 0) atomicExch(&p.status[1], 1);
+    if (leader) umma_commit(accum_bar);
+  } else if (is_conv) {
+    // ------------------------------ converters ------------------------------
+    // The X tile was written by TMA with the 128-byte swizzle: the 16-byte chunk c of row r sits at
+    // chunk position c ^ (r & 7), which also makes the row-per-thread reads conflict-free.
+    const int row = quad * 32 + lane;
+    const uint32_t sw = row & 7;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    bool ok = true;
+    for (int s = conv_set; s < n_steps; s += kConvSets) {
+      const int slot = s % kXSlots, aslot = s & (kASlots - 1);
+      // the activation slot is free once the MMAs of step s - kASlots are done (this warp confirmed the
+      // release of step s - kConvSets - kASlots on its previous turn, so the parity cannot alias)
+      if (s >= kASlots && !mbar_wait_warp(&empty_bar[(s - kASlots) % kXSlots], ((s - kASlots) / kXSlots) & 1)) { ok = false; break; }
+      if (!mbar_wait_warp(&full_bar[slot], (s / kXSlots) & 1)) { ok = false; break; }
+      const uint8_t* xrow = x_ring + slot * kXBytes + row * (kStepK * 2);
+      uint32_t r[32];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((c ^ sw) << 4));
+        r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
+      }
+      tmem_st_x32(a_tmem + aslot * kACols + lane_addr, r);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&afull_bar[aslot]);
+    }
+    failed |= !ok;
+    if (!ok && lane == 0) atomicExch(&p.status[3], 1);
+
+    // ------------------------------ epilogue ------------------------------
+    // the two warps of a lane quadrant take alternate accumulators
+    const uint32_t written = *s_written;
+    if (!mbar_wait_warp(accum_bar, 0)) {
+      failed = true;
+      if (lane == 0) atomicExch(&p.status[2], 1);
+    } else {
+      tc_fence_after_sync();
+      T* crow = static_cast<T*>(p.C) + ((long long)batch * p.M + m0 + row) * p.N;
+      for (int l = conv_set; l < nb_end - nb0; l += kConvSets) {
+        uint32_t r[32];
+        if ((written >> l) & 1u) {
+          tmem_ld_x32(tmem_base + lane_addr + l * kBlk, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0;
+        }
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float2 bv = *reinterpret_cast<const float2*>(&s_bias[l * kBlk + 2 * j]);
+          const float v0 = __uint_as_float(r[2 * j]) + bv.x, v1 = __uint_as_float(r[2 * j + 1]) + bv.y;
+          if constexpr (FMT == 0) {
+            __half2 h = __floats2half2_rn(v0, v1);
+            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        uint4* dst = reinterpret_cast<uint4*>(crow + (nb0 + l) * kBlk);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  sync_and_drain(failed);
+  if (warp == kMma0) {
+    tc_fence_after_sync();
+    tmem_dealloc<kTmemCols>(tmem_base);
+  }
+}
+
+template <int FMT>
+int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
+  CUtensorMap tm_x, tm_w;
+  {
+    const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.batch * p.M};
+    const uint64_t strides[1] = {(uint64_t)p.K * 2};
+    const uint32_t box[2] = {kStepK, kTileM};
+    int rc = make_tensor_map(&tm_x, p.A, p.dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != SPARTA_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {kBlk, (uint64_t)p.batch * p.val_stride_blocks * kBlk};
+    const uint64_t strides[1] = {kBlk * 2};
+    const uint32_t box[2] = {kBlk, kBlk};
+    int rc = make_tensor_map(&tm_w, p.B, p.dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc != SPARTA_OK) return rc;
+  }
+  DsdTcParams q;
+  q.row_ptr = p.ptr;
+  q.idx = static_cast<const int32_t*>(p.idx);
+  q.bias = p.bias;
+  q.C = p.C;
+  q.M = p.M; q.N = p.N; q.Kb = p.K / kBlk; q.Nb = p.N / kBlk;
+  q.val_stride_blocks = p.val_stride_blocks;
+  q.status = device_status_ptr();
+  if (!q.status) return SPARTA_ERR_DRIVER;
+  auto kern = bsmm_dsd_tc_kernel<FMT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  dim3 grid((q.Nb + kNP - 1) / kNP, p.M / kTileM, p.batch);
+  kern<<<grid, kThreads, kSmemTotal, st>>>(tm_x, tm_w, q);
+  return launch_status();
+}
+
+}  // namespace
+bool bsmm_tc_available() { return true; }
+
+bool dsd_tc_supported(const BsmmParams& p) {
+  if (p.mode != MODE_DSD || !p.trans_b || p.trans_a || !p.compressed || p.idx_is_64) return false;
+  if (p.dtype != SPARTA_F16 && p.dtype != SPARTA_BF16) return false;
+  if (p.BM != kTileM || p.BK != kBlk || p.BN != kBlk) return false;
+  if (p.M % kTileM || p.K % kBlk || p.N % kBlk) return false;
+  if (p.K / kBlk > kMaxKb || p.n_index_sets != 1 || p.val_stride_blocks <= 0) return false;
+  if ((long long)p.batch * p.val_stride_blocks * kBlk > 0x7fffffffll) return false;
+  if ((long long)p.batch * p.M > 0x7fffffffll || p.batch > 65535 || p.M / kTileM > 65535) return false;
+  if (!aligned(p.A, 16) || !aligned(p.B, 16) || !aligned(p.C, 16)) return false;
+  return true;
+}
+
+int dsd_tc_launch(const BsmmParams& p, cudaStream_t st) {
+  return p.dtype == SPARTA_F16 ? launch_dsd_tc<0>(p, st) : launch_dsd_tc<1>(p, st);
+}
+
+}  // namespace sparta

@@ -41,6 +41,9 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -75,6 +78,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     for (int i = 0; i < 16; ++i)
       if (mbar_try_wait_suspend(bar, parity, 4000u)) return true; else __nanosleep(100);
     if (global_timer_ns() - t0 > kWaitNanos) return false;
+  }
+}
+
+// The same wait called by all 32 lanes of a warp: returns one answer for the whole warp with the warp
+// reconverged.  Lanes leave the polling loop at different times, and the .sync.aligned tcgen05
+// instructions (ld, st, alloc) that usually follow need every lane at the instruction together.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
+  const bool ok = mbar_wait(bar, parity);
+  return __all_sync(0xffffffffu, ok);
+}
+
+// Last barrier of a kernel that used bounded waits; every thread passes whether one of its waits gave
+// up.  If any did, loads and MMAs of this CTA may still be in flight, and they must not land in shared
+// or tensor memory that no longer belongs to it: give them 200 us before the CTA lets go.
+__device__ __forceinline__ void sync_and_drain(bool failed) {
+  if (__syncthreads_or(failed ? 1 : 0)) {
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(2000);
+    __syncthreads();
   }
 }
 
