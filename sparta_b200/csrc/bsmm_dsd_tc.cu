@@ -38,7 +38,7 @@
 //                tcgen05.commit arrives on the step's "empty" mbarrier, which frees the X tile, the W
 //                blocks and the activation slot once all four have arrived.  One thread sustains about
 //                one MMA per 45 cycles, hence four issuers.
-//   warps 0-3, 12-15 afterwards: epilogue, tcgen05.ld -> + bias -> fp16 / bf16 -> global
+//   warps 0-3, 12-15 afterwards: epilogue, tcgen05.ld -> + bias -> fp16 / bf16 -> shared memory -> TMA store
 // Every mbarrier wait is bounded; a wait that runs out sets a status word and the CTA winds down.
 //
 // Replaces sparta_sparse_matmul_dsd.cuh.j2 / openai_sparse_matmul_dsd.cuh.j2 for this layout.
@@ -89,6 +89,7 @@ struct DsdTcParams {
 constexpr uint32_t kAccCols = kNP * kBlk;   // 384
 constexpr uint32_t kTmemCols = 512;
 static_assert(kAccCols + kASlots * kACols <= kTmemCols, "tensor memory budget");
+static_assert(2 * kXSlots >= kNP, "the epilogue stages the output tile in the X ring");
 
 // shared-memory carve-up (byte offsets from a 1 KB aligned base)
 constexpr int kOffX = 0;                                  // X ring   [kXSlots][128 rows x 128 B]
@@ -113,7 +114,7 @@ constexpr uint32_t mine_mask(int np, int issuers) {
 template <int FMT>
 __global__ void __launch_bounds__(kThreads, 1)
 bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                   DsdTcParams p) {
+                   const __grid_constant__ CUtensorMap tm_c, DsdTcParams p) {
   using T = typename std::conditional<FMT == 0, __half, __nv_bfloat16>::type;
   constexpr int NP = kNP;
   constexpr int kIssuers = kMmaWarps;
@@ -164,6 +165,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   if (warp == kProd0 && lane == 0) {
     prefetch_tensormap(&tm_x);
     prefetch_tensormap(&tm_w);
+    prefetch_tensormap(&tm_c);
   }
   if (warp == kMma0) tmem_alloc<kTmemCols>(tmem_holder);
   for (int k = threadIdx.x; k < 2 * n_pairs; k += kThreads) kmask[k] = 0;  // includes the pad block of an odd Kb
@@ -362,15 +364,19 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     if (!ok && lane == 0) atomicExch(&p.status[3], 1);
 
     // ------------------------------ epilogue ------------------------------
-    // the two warps of a lane quadrant take alternate accumulators
+    // Accumulators -> + bias -> 16 bit -> the idle X ring as six tiles of 128 rows x 64 columns in
+    // the 128-byte swizzle, then one TMA store per tile.  (Storing from registers, a lane per row,
+    // would touch 32 different lines with every instruction and took four times longer.)  The two
+    // warps of a lane quadrant take alternate pairs of accumulators.
     const uint32_t written = *s_written;
     if (!mbar_wait_warp(accum_bar, 0)) {
       failed = true;
       if (lane == 0) atomicExch(&p.status[2], 1);
     } else {
       tc_fence_after_sync();
-      T* crow = static_cast<T*>(p.C) + ((long long)batch * p.M + m0 + row) * p.N;
-      for (int l = conv_set; l < nb_end - nb0; l += kConvSets) {
+      const int n_acc = nb_end - nb0;
+      for (int l = 0; l < n_acc; ++l) {
+        if (((l >> 1) & 1) != conv_set) continue;
         uint32_t r[32];
         if ((written >> l) & 1u) {
           tmem_ld_x32(tmem_base + lane_addr + l * kBlk, r);
@@ -392,11 +398,23 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             packed[j] = *reinterpret_cast<uint32_t*>(&h);
           }
         }
-        uint4* dst = reinterpret_cast<uint4*>(crow + (nb0 + l) * kBlk);
+        // tile l / 2, row `row`, 16-byte chunks (l % 2) * 4 .. + 3, each at chunk position c ^ (row & 7)
+        uint8_t* trow = x_ring + (l >> 1) * kXBytes + row * 128;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t c = static_cast<uint32_t>((l & 1) * 4 + j) ^ sw;
+          *reinterpret_cast<uint4*>(trow + (c << 4)) =
+              make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+        }
       }
+      fence_proxy_async_smem();  // the tiles were written through the generic proxy, TMA reads through the async one
+    }
+    named_barrier_sync(1, 8 * 32);  // the eight epilogue warps
+    if (warp == 0 && lane == 0 && !failed) {
+      const int n_tiles = (nb_end - nb0 + 1) / 2;
+      for (int t = 0; t < n_tiles; ++t)
+        tma_store_2d(&tm_c, x_ring + t * kXBytes, (nb0 + 2 * t) * kBlk, batch * p.M + m0);
+      tma_store_commit_and_wait();
     }
   }
   tc_fence_before_sync();
@@ -424,6 +442,14 @@ int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
     int rc = make_tensor_map(&tm_w, p.B, p.dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc != SPARTA_OK) return rc;
   }
+  CUtensorMap tm_c;
+  {
+    const uint64_t dims[2] = {(uint64_t)p.N, (uint64_t)p.batch * p.M};
+    const uint64_t strides[1] = {(uint64_t)p.N * 2};
+    const uint32_t box[2] = {kStepK, kTileM};
+    int rc = make_tensor_map(&tm_c, p.C, p.dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != SPARTA_OK) return rc;
+  }
   DsdTcParams q;
   q.row_ptr = p.ptr;
   q.idx = static_cast<const int32_t*>(p.idx);
@@ -441,7 +467,7 @@ int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
     attr_set = true;
   }
   dim3 grid((q.Nb + kNP - 1) / kNP, p.M / kTileM, p.batch);
-  kern<<<grid, kThreads, kSmemTotal, st>>>(tm_x, tm_w, q);
+  kern<<<grid, kThreads, kSmemTotal, st>>>(tm_x, tm_w, tm_c, q);
   return launch_status();
 }
 
