@@ -238,6 +238,32 @@ def run_extras(device, peaks, flush, only=None):
     except Exception as e:
         extras['attention_b4h16s4096d64'] = {'error': repr(e)[:200]}
 
+    # the large attention configuration: bf16, 64 x 32 = 2048 heads, S 8192, D 128 (17 GB of q, k, v, o),
+    # same mask generator on a 128 x 128 grid of 64 x 64 blocks; one GPU holds all heads here, the
+    # multi-GPU form shards the head dimension with no exchange
+    try:
+        if not want('attention_large'):
+            raise KeyError('skipped')
+        heads, S, D = 2048, 8192, 128
+        dg = torch.Generator(device=device).manual_seed(2025)
+        q, k, v = (torch.randn((heads, S, D), generator=dg, device=device, dtype=torch.bfloat16) for _ in range(3))
+        amask = oracle.band_global_random_mask(S, S, 64, 8, 0.05, seed=0).to(device)
+        attn = sparta.nn.SparseAttention(mask=amask)
+        mm = {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': 64, 'BLOCK_SIZE_K_VALUE': 64, 'BLOCK_SIZE_N_VALUE': 64}
+        sm = {'_impl': 'sparta', 'BLOCK_SIZE_H_VALUE': 64, 'BLOCK_SIZE_W_VALUE': 64, 'ROW_TILE_VALUE': 4}
+        attn.build({'qk/forward:C': mm, 'sm/forward:y': sm, 'out/forward:C': mm}, sample_inputs=[q, k, v])
+        nnz = attn.get_sparse_indexes().block_nnz
+        ms = time_steps(lambda: attn(q, k, v), 3, 3, lambda: None) / 3  # inputs (17 GB) are far larger than L2
+        flops = 4.0 * heads * nnz * 64 * 64 * D
+        extras['attention_b64h32s8192d128_bf16'] = {
+            'fwd_ms': round(ms, 3), 'nnz_blocks': nnz, 'fused': bool(attn._use_fused),
+            'tflops': round(flops / ms / 1e9, 2), 'frac_tensor_peak': round(flops / ms / 1e9 / peaks['tflops'], 4),
+            'gbs': round(4.0 * heads * S * D * 2 / ms / 1e6, 1)}
+        del q, k, v, attn
+        torch.cuda.empty_cache()
+    except Exception as e:
+        extras['attention_b64h32s8192d128_bf16'] = {'error': repr(e)[:200]}
+
     # mask -> BCSR on the GPU: 32 masks of 2048 x 2048, 32x32 blocks, 90 % sparse
     try:
         if not want('convert'):
@@ -343,7 +369,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-extras', action='store_true')
     ap.add_argument('--extras', default=None,
-                    help='comma list of extra measurements to run: linear,attention,convert,readme (default all)')
+                    help='comma list of extra measurements to run: linear,attention,attention_large,convert,readme (default all)')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
 
