@@ -24,8 +24,11 @@ struct BsmmParams {
   long long ptr_stride, idx_stride, val_stride_blocks, grid_blocks_hint;
 };
 
-// FMA kernel: every layout.  Returns a status code of sparta_b200.h.
+// FMA kernels: bsmm_simt takes every layout (and hands the SparseLinear layout with small square
+// blocks to the register-tiled dsd kernel).  Return a status code of sparta_b200.h.
 int bsmm_simt(const BsmmParams& p, cudaStream_t st);
+bool dsd_fma_supported(const BsmmParams& p);
+int dsd_fma_launch(const BsmmParams& p, cudaStream_t st);
 
 // tcgen05 kernels: return SPARTA_ERR_UNSUPPORTED when the configuration is outside their coverage.
 bool dsd_tc_supported(const BsmmParams& p);

@@ -1,0 +1,269 @@
+// dsd on the FMA units for the SparseLinear layout with small square blocks (8, 16 or 32), any dtype
+// with fp32 accumulation: C[m, n] = sum over kept K-blocks k of row-block n of X[m, k-block] . W_block^T.
+//
+// The generic FMA kernel gives every (row tile, block row) its own CTA and stages both operands
+// through shared memory with two barriers per K-block; with 8 x 8 blocks that is 64 x 8 outputs and
+// eight multiply-adds per thread between barriers.  Here a thread owns one token row and 64 output
+// columns (a panel of 64 / B block rows of W) in registers, and a CTA owns 128 (or 64) such rows, each
+// shared by two threads that take alternate K-blocks and add their partial sums at the end (twice the
+// warps for the same loads: with one thread per row an SM would hold only three or four warps):
+//   * the prologue turns the BCSR rows of the panel into kmask[k] (which block rows keep K-block k) and
+//     wpos[k][l] (where that block sits in the value array), so the main loop has no index search;
+//   * K is walked in chunks of 64 values.  A chunk's activations (rows x 64) and its kept W blocks
+//     (at most 64 x 64 values, each block in a fixed slot) are brought into shared memory with
+//     cp.async, double-buffered, so the loads of the next chunk overlap the multiply-adds of this one;
+//   * a thread reads its own activations with conflict-free vector loads (padded rows) and the weights
+//     with broadcast loads; the block-row loop is unrolled so that the accumulators stay in registers.
+//
+// Replaces sparta_sparse_matmul_dsd.cuh.j2 for these configurations (the reference covers 8 x 8 masks
+// with 16 x 16 or larger tiles, sparta/specializer/kernels/matmul.py:53-97).
+#include "bsmm.cuh"
+
+namespace sparta {
+namespace {
+
+constexpr int kPanelCols = 64;   // output columns per thread
+constexpr int kMaxKbFma = 1024;  // K-blocks the schedule can hold
+
+template <typename T, int N>
+__device__ __forceinline__ void load_floats(const T* src, float (&out)[N]) {
+  // N values starting at a 16-byte aligned address, as fp32
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+      const float4 v = *(reinterpret_cast<const float4*>(src) + i);
+      out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < N / 8; ++i) {
+      const uint4 v = *(reinterpret_cast<const uint4*>(src) + i);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        T lo, hi;
+        const uint16_t l16 = static_cast<uint16_t>(w[j] & 0xffffu), h16 = static_cast<uint16_t>(w[j] >> 16);
+        memcpy(&lo, &l16, 2);
+        memcpy(&hi, &h16, 2);
+        out[8 * i + 2 * j] = to_float(lo);
+        out[8 * i + 2 * j + 1] = to_float(hi);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(gsrc)
+               : "memory");
+}
+
+constexpr int kChunkK = 64;  // K values per chunk
+
+template <int TM, typename T>
+struct FmaSmem {
+  static constexpr int kXRow = kChunkK * (int)sizeof(T) + 16;  // padded row: conflict-free 16-byte reads, one row per lane
+  static constexpr int kXBytes = TM * kXRow;
+  static constexpr int kWBytes = kChunkK * kPanelCols * (int)sizeof(T);  // (64 / B)^2 slots of B x B values
+  static constexpr int kStage = kXBytes + kWBytes;
+  static constexpr int kTotal = 2 * kStage;
+};
+
+template <int B, int TM, typename T>
+__global__ void __launch_bounds__(2 * TM) bsmm_dsd_fma_kernel(BsmmParams p) {
+  constexpr int NT = 2 * TM;          // threads: two per row
+  constexpr int P = kPanelCols / B;   // block rows of W per panel
+  constexpr int KC = kChunkK / B;     // K-blocks per chunk
+  using S = FmaSmem<TM, T>;
+  extern __shared__ __align__(16) uint8_t stage_mem[];
+  __shared__ uint32_t kmask[kMaxKbFma];
+  __shared__ uint16_t wpos[kMaxKbFma * P];
+  __shared__ int s_range[2];
+
+  const int panel = blockIdx.x, m0 = blockIdx.y * TM, batch = blockIdx.z;
+  const int Nb = p.N / B, Kb = p.K / B;
+  const int nb0 = panel * P, nb_end = min(nb0 + P, Nb);
+  if (threadIdx.x == 0) {
+    s_range[0] = p.ptr[nb0];
+    s_range[1] = p.ptr[nb_end];
+  }
+  for (int k = threadIdx.x; k < Kb; k += NT) kmask[k] = 0;
+  __syncthreads();
+  const int e0 = s_range[0];
+  const int32_t* idx = static_cast<const int32_t*>(p.idx);
+  for (int e = e0 + threadIdx.x; e < s_range[1]; e += NT) {
+    const int v = __ldg(idx + e);
+    const int k = v & 0xffff, l = (v >> 16) - nb0;
+    if (k < Kb && l >= 0 && l < P) {  // caller-provided indexes never address shared memory unchecked
+      atomicOr(&kmask[k], 1u << l);
+      wpos[k * P + l] = static_cast<uint16_t>(e - e0);
+    }
+  }
+  __syncthreads();
+
+  const T* xtile = static_cast<const T*>(p.A) + ((long long)batch * p.M + m0) * p.K;
+  const T* wbase = static_cast<const T*>(p.B) + ((long long)batch * p.val_stride_blocks + e0) * (B * B);
+  const int n_chunks = p.K / kChunkK;
+
+  // staging: every thread copies the same 16-byte piece of successive rows / block slots, so the
+  // index arithmetic is done once
+  constexpr int XP = kChunkK * (int)sizeof(T) / 16;  // 16-byte pieces per row
+  constexpr int SP = B * B * (int)sizeof(T) / 16;    // pieces per block slot
+  constexpr int WP = S::kWBytes / 16;
+  static_assert(NT % XP == 0 && (TM * XP) % NT == 0 && WP % NT == 0, "whole passes over the pieces");
+  const int x_r0 = threadIdx.x / XP, x_q = threadIdx.x % XP;
+  const uint8_t* x_src0 = reinterpret_cast<const uint8_t*>(xtile + (long long)x_r0 * p.K) + x_q * 16;
+  const long long x_step = (long long)(NT / XP) * p.K * (long long)sizeof(T);
+  auto issue = [&](int c, int buf) {
+    uint8_t* xs = stage_mem + buf * S::kStage;
+    uint8_t* ws = xs + S::kXBytes;
+    const uint8_t* src = x_src0 + (long long)c * kChunkK * sizeof(T);
+    uint8_t* dst = xs + x_r0 * S::kXRow + x_q * 16;
+#pragma unroll
+    for (int it = 0; it < TM * XP / NT; ++it) {
+      cp_async_16(dst, src);
+      src += x_step;
+      dst += (NT / XP) * S::kXRow;
+    }
+#pragma unroll
+    for (int it = 0; it < WP / NT; ++it) {
+      const int i = threadIdx.x + it * NT;
+      const int slot = i / SP, within = i % SP;  // powers of two
+      const int kc = slot / P, l = slot % P;
+      const int k = c * KC + kc;
+      if ((kmask[k] >> l) & 1u)
+        cp_async_16(ws + i * 16, reinterpret_cast<const uint8_t*>(wbase + (long long)wpos[k * P + l] * (B * B)) + within * 16);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  float acc[kPanelCols];
+#pragma unroll
+  for (int j = 0; j < kPanelCols; ++j) acc[j] = 0.f;
+
+  if (n_chunks > 0) issue(0, 0);
+  for (int c = 0; c < n_chunks; ++c) {
+    if (c + 1 < n_chunks) {
+      issue(c + 1, (c + 1) & 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const uint8_t* xs = stage_mem + (c & 1) * S::kStage;
+    const uint8_t* ws = xs + S::kXBytes;
+    const T* xrow = reinterpret_cast<const T*>(xs + (threadIdx.x % TM) * S::kXRow);
+#pragma unroll 1
+    for (int kc = threadIdx.x / TM; kc < KC; kc += 2) {  // the two threads of a row take alternate K-blocks
+      const uint32_t m = kmask[c * KC + kc];  // the same for every thread of the CTA
+      if (!m) continue;
+      float x[B];
+      load_floats<T, B>(xrow + kc * B, x);
+#pragma unroll
+      for (int l = 0; l < P; ++l) {
+        if (!((m >> l) & 1u)) continue;
+        const T* wb = reinterpret_cast<const T*>(ws) + (kc * P + l) * (B * B);  // stored [n][k], row-major
+#pragma unroll
+        for (int n = 0; n < B; ++n) {
+          float w[B];
+          load_floats<T, B>(wb + n * B, w);
+          float s = acc[l * B + n];
+#pragma unroll
+          for (int kk = 0; kk < B; ++kk) s = fmaf(x[kk], w[kk], s);
+          acc[l * B + n] = s;
+        }
+      }
+    }
+    __syncthreads();  // the buffer is refilled by the next iteration's issue
+  }
+
+  // the second thread of every row hands its partial sums over through the (now idle) staging memory
+  float* red = reinterpret_cast<float*>(stage_mem);
+  static_assert(S::kTotal >= TM * (kPanelCols + 1) * 4, "staging memory holds the partial sums");
+  if (threadIdx.x >= TM) {
+#pragma unroll
+    for (int j = 0; j < kPanelCols; ++j) red[j * TM + (threadIdx.x - TM)] = acc[j];
+  }
+  __syncthreads();
+  if (threadIdx.x >= TM) return;
+#pragma unroll
+  for (int j = 0; j < kPanelCols; ++j) acc[j] += red[j * TM + threadIdx.x];
+
+  // epilogue: + bias, convert, 16-byte stores along the row
+  const int row = m0 + threadIdx.x;
+  const int n0 = nb0 * B;
+  const int n_cols = (nb_end - nb0) * B;
+  const T* bias = p.bias ? static_cast<const T*>(p.bias) + (long long)batch * p.N + n0 : nullptr;
+  T* crow = static_cast<T*>(p.C) + ((long long)batch * p.M + row) * p.N + n0;
+  constexpr int kVec = 16 / sizeof(T);
+#pragma unroll
+  for (int j0 = 0; j0 < kPanelCols; j0 += kVec) {
+    if (j0 < n_cols) {
+      alignas(16) T out[kVec];
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) {
+        float v = acc[j0 + j];
+        if (bias) v += to_float(bias[j0 + j]);
+        out[j] = from_float<T>(v);
+      }
+      *reinterpret_cast<uint4*>(crow + j0) = *reinterpret_cast<const uint4*>(out);
+    }
+  }
+}
+
+template <int B, int TM, typename T>
+int launch_tm(const BsmmParams& p, int panels, cudaStream_t st) {
+  using S = FmaSmem<TM, T>;
+  auto kern = bsmm_dsd_fma_kernel<B, TM, T>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  kern<<<dim3(panels, p.M / TM, p.batch), 2 * TM, S::kTotal, st>>>(p);
+  return launch_status();
+}
+
+template <int B, typename T>
+int launch_b(const BsmmParams& p, cudaStream_t st) {
+  const int P = kPanelCols / B;
+  const int panels = (p.N / B + P - 1) / P;
+  if (p.M % 128 == 0 && (long long)panels * (p.M / 128) * p.batch >= kNumSMs / 2)
+    return launch_tm<B, 128, T>(p, panels, st);
+  return launch_tm<B, 64, T>(p, panels, st);
+}
+
+template <typename T>
+int launch_t(const BsmmParams& p, cudaStream_t st) {
+  switch (p.BN) {
+    case 8: return launch_b<8, T>(p, st);
+    case 16: return launch_b<16, T>(p, st);
+    case 32: return launch_b<32, T>(p, st);
+    default: return SPARTA_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace
+
+bool dsd_fma_supported(const BsmmParams& p) {
+  if (p.mode != MODE_DSD || !p.trans_b || p.trans_a || !p.compressed || p.idx_is_64) return false;
+  if (p.BN != p.BK || (p.BN != 8 && p.BN != 16 && p.BN != 32)) return false;
+  if (p.M % 64 || p.K % kChunkK || p.N % p.BN) return false;
+  if (p.K / p.BK > kMaxKbFma || p.n_index_sets != 1 || p.val_stride_blocks <= 0 || !p.ptr) return false;
+  if (p.batch > 65535 || p.M / 64 > 65535) return false;
+  if (!aligned(p.A, 16) || !aligned(p.B, 16) || !aligned(p.C, 16)) return false;
+  if (p.bias && !aligned(p.bias, 4)) return false;
+  return true;
+}
+
+int dsd_fma_launch(const BsmmParams& p, cudaStream_t st) {
+  switch (p.dtype) {
+    case SPARTA_F32: return launch_t<float>(p, st);
+    case SPARTA_F16: return launch_t<__half>(p, st);
+    case SPARTA_BF16: return launch_t<__nv_bfloat16>(p, st);
+    default: return SPARTA_ERR_BAD_ARG;
+  }
+}
+
+}  // namespace sparta

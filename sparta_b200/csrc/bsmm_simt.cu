@@ -178,6 +178,7 @@ int launch(const BsmmParams& p, cudaStream_t st) {
 }  // namespace
 
 int bsmm_simt(const BsmmParams& p, cudaStream_t st) {
+  if (dsd_fma_supported(p)) return dsd_fma_launch(p, st);
   if (p.BM > kMaxTile || p.BN > kMaxTile || p.BK > kMaxTile) return SPARTA_ERR_UNSUPPORTED;
   if (p.BM < 4 || p.BN < 4 || p.BK < 4) return SPARTA_ERR_UNSUPPORTED;
   if (p.batch > 65535 || p.M / p.BM > 65535) return SPARTA_ERR_SHAPE;

@@ -126,6 +126,8 @@ class SparseMatMulKernel(KernelBase):
         impl = _FAMILY[self._family]
         by_row = self._bcs_mode == 'BCSR'
 
+        cache = {}
+
         def matmul_func(A: torch.Tensor, B: torch.Tensor, bias: torch.Tensor = None):
             _lib.require_cuda(A, B, bias)
             idx = port.indexes
@@ -147,19 +149,27 @@ class SparseMatMulKernel(KernelBase):
                 ptr_t, idx_t, is64 = idx.col_ptr, idx.bcsc_buf, idx.BCSR
             if idx.batched:
                 assert idx.n_masks == batch, 'per-batch masks need one mask per batch element'
-            args = _lib.BsmmArgs(
-                A=A.data_ptr(), B=B.data_ptr(), bias=_lib.ptr(bias.contiguous()) if biased else None,
-                C=C.data_ptr(), ptr=ptr_t.data_ptr(), idx=idx_t.data_ptr(), nnz=idx.nnz_dev.data_ptr(),
-                batch=batch, M=M, K=K, N=N, BM=BM, BK=BK, BN=BN,
-                trans_a=int(trans_a), trans_b=int(trans_b), compressed=int(compressed),
-                idx_is_64=int(is64), dtype=_lib.dtype_code(A), impl=impl,
-                n_index_sets=idx.n_masks if idx.batched else 1,
-                ptr_stride=ptr_t.shape[-1], idx_stride=idx.capacity,
-                val_stride_blocks=stride if compressed else 0,
-                grid_blocks_hint=idx.capacity if idx.batched else max(stride, 1),
-            )
-            with torch.cuda.device(A.device):
+            key = (ptr_t.data_ptr(), idx_t.data_ptr(), idx.nnz_dev.data_ptr(), stride, idx.capacity, batch, A.dtype)
+            args = cache.get('args') if cache.get('key') == key else None
+            if args is None:  # everything but the data pointers is fixed until the indexes, batch or dtype change
+                args = _lib.BsmmArgs(
+                    ptr=ptr_t.data_ptr(), idx=idx_t.data_ptr(), nnz=idx.nnz_dev.data_ptr(),
+                    batch=batch, M=M, K=K, N=N, BM=BM, BK=BK, BN=BN,
+                    trans_a=int(trans_a), trans_b=int(trans_b), compressed=int(compressed),
+                    idx_is_64=int(is64), dtype=_lib.dtype_code(A), impl=impl,
+                    n_index_sets=idx.n_masks if idx.batched else 1,
+                    ptr_stride=ptr_t.shape[-1], idx_stride=idx.capacity,
+                    val_stride_blocks=stride if compressed else 0,
+                    grid_blocks_hint=idx.capacity if idx.batched else max(stride, 1),
+                )
+                cache['key'], cache['args'] = key, args
+            args.A, args.B, args.C = A.data_ptr(), B.data_ptr(), C.data_ptr()
+            args.bias = _lib.ptr(bias.contiguous()) if biased else None
+            if A.device.index == torch.cuda.current_device():
                 _lib.check(entry(args, _lib.stream_ptr(A.device)), _ENTRY[mode])
+            else:
+                with torch.cuda.device(A.device):
+                    _lib.check(entry(args, _lib.stream_ptr(A.device)), _ENTRY[mode])
             return C
 
         self._func = matmul_func
