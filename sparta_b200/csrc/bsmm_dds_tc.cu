@@ -26,14 +26,17 @@ constexpr int kBlk = 32;          // output block edge
 constexpr int kTileM = 128;       // rows per CTA (four block rows)
 constexpr int kGroup = 8;         // block columns per CTA
 constexpr int kChunkK = 64;       // K elements per pipeline stage (128 bytes)
-constexpr int kStages = 4;
 constexpr int kABytes = kTileM * kChunkK * 2;         // 16 KB
 constexpr int kBBlockBytes = kBlk * kChunkK * 2;      // 4 KB per gathered column block
 constexpr int kStageBytes = kABytes + kGroup * kBBlockBytes;  // 48 KB
 constexpr int kMaxNb = 1024;      // block columns (N <= 32768)
 constexpr int kThreads = 192;
-constexpr int kSmem = kStages * kStageBytes + kMaxNb /* column masks */ + kMaxNb * 2 /* column list */ +
-                      512 /* barriers, positions */ + 1024 /* align */;
+// STAGES = 4 (197 KB, one CTA per SM) for long K; STAGES = 2 (101 KB, two CTAs per SM, so that the
+// prologue and epilogue of one overlap the main loop of the other) when K has at most two chunks.
+constexpr int smem_bytes(int stages) {
+  return stages * kStageBytes + kMaxNb /* column masks */ + kMaxNb * 2 /* column list */ +
+         512 /* barriers, positions */ + 1024 /* align */;
+}
 
 struct DdsTcParams {
   const int32_t* row_ptr;
@@ -47,20 +50,20 @@ struct DdsTcParams {
   int32_t* status;
 };
 
-template <int FMT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int FMT, int STAGES>
+__global__ void __launch_bounds__(kThreads, STAGES == 2 ? 2 : 1)
 bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    DdsTcParams p) {
   using T = typename std::conditional<FMT == 0, __half, __nv_bfloat16>::type;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stages = smem;
-  uint8_t* cmask = smem + kStages * kStageBytes;                      // [Nb] 4 presence bits per column
+  uint8_t* cmask = smem + STAGES * kStageBytes;                      // [Nb] 4 presence bits per column
   uint16_t* clist = reinterpret_cast<uint16_t*>(cmask + kMaxNb);      // needed columns, ascending
   uint8_t* ctl = reinterpret_cast<uint8_t*>(clist + kMaxNb);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctl);              // [kStages]
-  uint64_t* empty_bar = full_bar + kStages;                           // [kStages]
-  uint64_t* accum_bar = empty_bar + kStages;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctl);              // [STAGES]
+  uint64_t* empty_bar = full_bar + STAGES;                           // [STAGES]
+  uint64_t* accum_bar = empty_bar + STAGES;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum_bar + 1);
   int* s_count = reinterpret_cast<int*>(tmem_holder + 1);
   int* s_range = s_count + 1;                                         // [2]
@@ -111,7 +114,7 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       if (clist[c_first + l] == c) s_pos[((v >> 16) - mb0) * kGroup + l] = e;
   }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -135,8 +138,8 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     const int col = lane < ncols ? clist[c_first + lane] : 0;
     bool ok = true;
     for (int c = 0; c < nchunks; ++c) {
-      const int s = c % kStages;
-      if (!mbar_wait(&empty_bar[s], ((c / kStages) & 1) ^ 1)) { ok = false; break; }
+      const int s = c % STAGES;
+      if (!mbar_wait(&empty_bar[s], ((c / STAGES) & 1) ^ 1)) { ok = false; break; }
       uint8_t* st = stages + s * kStageBytes;
       if (lane == 0) {
         mbar_arrive_expect_tx(&full_bar[s], kABytes + ncols * kBBlockBytes);
@@ -162,8 +165,8 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     const uint32_t base = smem_u32(stages) >> 4;
     bool ok = true;
     for (int c = 0; c < nchunks; ++c) {
-      const int s = c % kStages;
-      if (!mbar_wait(&full_bar[s], (c / kStages) & 1)) { ok = false; break; }
+      const int s = c % STAGES;
+      if (!mbar_wait(&full_bar[s], (c / STAGES) & 1)) { ok = false; break; }
       tc_fence_after_sync();
       if (lane == 0) {
         const uint32_t a_lo = base + ((s * kStageBytes) >> 4);
@@ -230,7 +233,7 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   }
 }
 
-template <int FMT>
+template <int FMT, int STAGES>
 int launch_dds(const BsmmParams& p, cudaStream_t st) {
   CUtensorMap tm_a, tm_b;
   {
@@ -264,7 +267,8 @@ int launch_dds(const BsmmParams& p, cudaStream_t st) {
   q.ptr_stride = p.ptr_stride; q.idx_stride = p.idx_stride; q.val_stride_blocks = p.val_stride_blocks;
   q.status = device_status_ptr();
   if (!q.status) return SPARTA_ERR_DRIVER;
-  auto kern = bsmm_dds_tc_kernel<FMT>;
+  auto kern = bsmm_dds_tc_kernel<FMT, STAGES>;
+  constexpr int kSmem = smem_bytes(STAGES);
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
@@ -292,7 +296,8 @@ bool dds_tc_supported(const BsmmParams& p) {
 }
 
 int dds_tc_launch(const BsmmParams& p, cudaStream_t st) {
-  return p.dtype == SPARTA_F16 ? launch_dds<0>(p, st) : launch_dds<1>(p, st);
+  if (p.K <= 2 * kChunkK) return p.dtype == SPARTA_F16 ? launch_dds<0, 2>(p, st) : launch_dds<1, 2>(p, st);
+  return p.dtype == SPARTA_F16 ? launch_dds<0, 4>(p, st) : launch_dds<1, 4>(p, st);
 }
 
 }  // namespace sparta

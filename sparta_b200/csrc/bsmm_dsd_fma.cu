@@ -11,7 +11,8 @@
 //     wpos[k][l] (where that block sits in the value array), so the main loop has no index search;
 //   * K is walked in chunks of 64 values.  A chunk's activations (rows x 64) and its kept W blocks
 //     (at most 64 x 64 values, each block in a fixed slot) are brought into shared memory with
-//     cp.async, double-buffered, so the loads of the next chunk overlap the multiply-adds of this one;
+//     cp.async, three stages deep, so the loads of the next two chunks overlap the multiply-adds of this
+//     one (a chunk's arithmetic is shorter than the latency of its loads);
 //   * a thread reads its own activations with conflict-free vector loads (padded rows) and the weights
 //     with broadcast loads; the block-row loop is unrolled so that the accumulators stay in registers.
 //
@@ -66,7 +67,8 @@ struct FmaSmem {
   static constexpr int kXBytes = TM * kXRow;
   static constexpr int kWBytes = kChunkK * kPanelCols * (int)sizeof(T);  // (64 / B)^2 slots of B x B values
   static constexpr int kStage = kXBytes + kWBytes;
-  static constexpr int kTotal = 2 * kStage;
+  static constexpr int kStages = 3;  // chunks in flight: one being used, two on their way
+  static constexpr int kTotal = kStages * kStage;
 };
 
 template <int B, int TM, typename T>
@@ -141,16 +143,18 @@ __global__ void __launch_bounds__(2 * TM) bsmm_dsd_fma_kernel(BsmmParams p) {
 #pragma unroll
   for (int j = 0; j < kPanelCols; ++j) acc[j] = 0.f;
 
-  if (n_chunks > 0) issue(0, 0);
+  // every iteration commits exactly one group (an empty one past the end), so "all but the newest
+  // kStages - 2 groups are complete" always means that chunk c has landed
+  for (int c = 0; c < S::kStages - 1; ++c) {
+    if (c < n_chunks) issue(c, c);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   for (int c = 0; c < n_chunks; ++c) {
-    if (c + 1 < n_chunks) {
-      issue(c + 1, (c + 1) & 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
-    const uint8_t* xs = stage_mem + (c & 1) * S::kStage;
+    asm volatile("cp.async.wait_group %0;" ::"n"(S::kStages - 2) : "memory");
+    __syncthreads();  // chunk c is visible to everyone, and everyone is done with the stage refilled below
+    if (c + S::kStages - 1 < n_chunks) issue(c + S::kStages - 1, (c + S::kStages - 1) % S::kStages);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    const uint8_t* xs = stage_mem + (c % S::kStages) * S::kStage;
     const uint8_t* ws = xs + S::kXBytes;
     const T* xrow = reinterpret_cast<const T*>(xs + (threadIdx.x % TM) * S::kXRow);
 #pragma unroll 1
@@ -174,8 +178,9 @@ __global__ void __launch_bounds__(2 * TM) bsmm_dsd_fma_kernel(BsmmParams p) {
         }
       }
     }
-    __syncthreads();  // the buffer is refilled by the next iteration's issue
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();  // all copies have landed and all reads of the staging memory are done
 
   // the second thread of every row hands its partial sums over through the (now idle) staging memory
   float* red = reinterpret_cast<float*>(stage_mem);
