@@ -54,27 +54,31 @@ using namespace tc;
 
 constexpr int kBlk = 32;            // BCSR block edge (K and N)
 constexpr int kTileM = 128;         // token rows per CTA
-constexpr int kStepK = 2 * kBlk;    // K values per step: an aligned pair of K-blocks
-constexpr int kXBytes = kTileM * kStepK * 2;  // 16 KB: 128 rows x 128 B
+constexpr int kG = 2;               // K-blocks per step (2 or 4; 4 halves the number of steps and measured the same)
+constexpr int kSubK = 2 * kBlk;     // K values of one X sub-tile: 128-byte rows, the widest swizzled TMA box
+constexpr int kSubTiles = kG / 2;   // X sub-tiles per step
+constexpr int kSubBytes = kTileM * kSubK * 2;  // 16 KB: 128 rows x 128 B
+constexpr int kStepK = kG * kBlk;   // K values per step
+constexpr int kXBytes = kSubTiles * kSubBytes;
 constexpr int kWBytes = kBlk * kBlk * 2;      // 2 KB
 constexpr int kACols = kStepK / 2;  // tensor-memory columns of one activation tile (two 16-bit values per column)
 constexpr int kNP = 12;             // block columns per CTA
-constexpr int kMaxKb = 1024;        // K-blocks the schedule can hold (K <= 32768)
-constexpr int kMaxSteps = kMaxKb / 2;
-constexpr int kXSlots = 6;          // steps whose loads (X tile, W blocks) are in flight
-constexpr int kASlots = 4;          // steps whose activations sit in tensor memory; a power of two
-constexpr int kWSlots = 40;         // W blocks in flight
+constexpr int kMaxKb = kG == 2 ? 1024 : 512;  // K-blocks the schedule can hold (K <= 32768 or 16384): shared-memory budget
+constexpr int kMaxSteps = kMaxKb / kG;
+constexpr int kXSlots = 12 / kG;    // steps whose loads (X tile, W blocks) are in flight: 96 KB of X
+constexpr int kASlots = 8 / kG;     // steps whose activations sit in tensor memory (128 columns); a power of two
+constexpr int kWSlots = kG == 2 ? 40 : 48;    // W blocks in flight
 constexpr int kMmaWarps = 12;       // MMA-issuing warps: one per accumulator
 constexpr int kConvSets = 2;        // converter warp sets (four warps each) that alternate steps
-constexpr int kProdWarps = 4;       // TMA-issuing warps; at most kXSlots (see the producers' wait)
-constexpr int kProd0 = 4;           // first producer warp
-constexpr int kMma0 = kProd0 + kProdWarps;   // first MMA-issuing warp
+constexpr int kProdWarps = kXSlots < 4 ? kXSlots : 4;  // TMA-issuing warps; at most kXSlots (see the producers' wait)
+constexpr int kMma0 = 4;            // first MMA-issuing warp
 constexpr int kConv1 = kMma0 + kMmaWarps;    // first warp of the second converter set (a multiple of 4)
-constexpr int kThreads = 32 * (kConv1 + 4);  // 768
+constexpr int kProd0 = kConv1 + 4;  // first producer warp
+constexpr int kThreads = 32 * (kProd0 + kProdWarps);
 static_assert(kProdWarps <= kXSlots && kASlots <= kXSlots, "a producer may run at most one ring turn ahead of the release it waits for");
 static_assert(kConv1 % 4 == 0, "converter warps must map onto their tensor-memory lane quadrant");
 static_assert(kNP <= 12 && kNP % kMmaWarps == 0, "a step record packs two 12-bit block masks");
-static_assert(kWSlots >= 2 * kNP && kWSlots < 64, "a step's W blocks must fit the ring; its position packs into 6 bits");
+static_assert(kWSlots >= kG * kNP && kWSlots < 64, "a step's W blocks must fit the ring; its position packs into 6 bits");
 
 struct DsdTcParams {
   const int32_t* row_ptr;
@@ -89,7 +93,7 @@ struct DsdTcParams {
 constexpr uint32_t kAccCols = kNP * kBlk;   // 384
 constexpr uint32_t kTmemCols = 512;
 static_assert(kAccCols + kASlots * kACols <= kTmemCols, "tensor memory budget");
-static_assert(2 * kXSlots >= kNP, "the epilogue stages the output tile in the X ring");
+static_assert(kXSlots * kXBytes >= (kNP / 2) * kSubBytes, "the epilogue stages the output tile in the X ring");
 
 // shared-memory carve-up (byte offsets from a 1 KB aligned base)
 constexpr int kOffX = 0;                                  // X ring   [kXSlots][128 rows x 128 B]
@@ -99,11 +103,12 @@ constexpr int kOffSrc = kOffMask + kMaxKb * 4;            // wsrc     [Kb][kNP] 
 constexpr int kOffStep = kOffSrc + kMaxKb * kNP * 2;      // step_kp  [steps]     u16: K-pair index
 constexpr int kOffCum = kOffStep + kMaxSteps * 2;         // cum_w    [steps + 1] u16: W blocks of all earlier steps
 constexpr int kOffWait = kOffCum + (kMaxSteps + 8) * 2;   // wait_for [steps]     s16
-constexpr int kOffRec = kOffWait + kMaxSteps * 2;         // rec      [steps]     u32: mask0 | mask1 << 12 | ring pos << 24
-constexpr int kOffBias = kOffRec + kMaxSteps * 4;         // bias     [kNP * 32]  f32
+constexpr int kOffRec = (kOffWait + kMaxSteps * 2 + 7) / 8 * 8;  // rec [steps] u64: 12-bit block mask per K-block | ring pos << 48
+constexpr int kOffBias = kOffRec + kMaxSteps * 8;         // bias     [kNP * 32]  f32
 constexpr int kOffCtl = kOffBias + kNP * kBlk * 4;        // mbarriers and scalars
 constexpr int kSmemTotal = kOffCtl + 512 + 1024 /* alignment slack */;
-static_assert(kOffRec % 4 == 0 && kOffBias % 8 == 0 && kOffCtl % 8 == 0, "alignment of the shared-memory tables");
+static_assert(kOffRec % 8 == 0 && kOffBias % 8 == 0 && kOffCtl % 8 == 0, "alignment of the shared-memory tables");
+static_assert(kSmemTotal <= 227 * 1024, "shared memory budget");
 
 constexpr uint32_t mine_mask(int np, int issuers) {
   uint32_t m = 0;
@@ -130,7 +135,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   uint16_t* step_kp = reinterpret_cast<uint16_t*>(smem + kOffStep);
   uint16_t* cum_w = reinterpret_cast<uint16_t*>(smem + kOffCum);
   int16_t* wait_for = reinterpret_cast<int16_t*>(smem + kOffWait);
-  uint32_t* rec = reinterpret_cast<uint32_t*>(smem + kOffRec);
+  uint64_t* rec = reinterpret_cast<uint64_t*>(smem + kOffRec);
   float* s_bias = reinterpret_cast<float*>(smem + kOffBias);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kOffCtl);  // [kXSlots] loads of a step have landed
   uint64_t* empty_bar = full_bar + kXSlots;                // [kXSlots] MMAs of a step have read their operands
@@ -145,10 +150,10 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const int panel = blockIdx.x, m0 = blockIdx.y * kTileM, batch = blockIdx.z;
   const int nb0 = panel * NP;
   const int nb_end = min(nb0 + NP, p.Nb);
-  const bool is_conv = warp < 4 || warp >= kConv1;
+  const bool is_conv = warp < 4 || (warp >= kConv1 && warp < kProd0);
   const int conv_set = warp < 4 ? 0 : 1;
   const int quad = warp & 3;  // tensor-memory lane quadrant this warp may access
-  const int n_pairs = (p.Kb + 1) / 2;
+  const int n_pairs = (p.Kb + kG - 1) / kG;  // K-groups (steps before the empty ones are dropped)
 
   // ------------------------------ prologue: barriers, tensor memory, schedule ------------------------------
   if (threadIdx.x == 0) {
@@ -168,7 +173,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     prefetch_tensormap(&tm_c);
   }
   if (warp == kMma0) tmem_alloc<kTmemCols>(tmem_holder);
-  for (int k = threadIdx.x; k < 2 * n_pairs; k += kThreads) kmask[k] = 0;  // includes the pad block of an odd Kb
+  for (int k = threadIdx.x; k < kG * n_pairs; k += kThreads) kmask[k] = 0;  // includes the pad blocks of the last group
   {
     const T* bias = p.bias ? static_cast<const T*>(p.bias) + (long long)batch * p.N : nullptr;
     for (int j = threadIdx.x; j < NP * kBlk; j += kThreads) {
@@ -194,11 +199,18 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     uint32_t wr = 0;
     for (int c = 0; c < n_pairs; c += 32) {
       const int kp = c + lane;
-      const uint32_t m = kp < n_pairs ? (kmask[2 * kp] | (kmask[2 * kp + 1] << NP)) : 0u;
-      wr |= (m | (m >> NP)) & kLow;
+      uint32_t m = 0u;  // which row-blocks keep any of the group's K-blocks; w: how many blocks in all
+      int w = 0;
+      if (kp < n_pairs) {
+#pragma unroll
+        for (int j = 0; j < kG; ++j) {
+          m |= kmask[kG * kp + j];
+          w += __popc(kmask[kG * kp + j]);
+        }
+      }
+      wr |= m;
       const unsigned bal = __ballot_sync(0xffffffffu, m != 0u);
       const int ord = base + __popc(bal & ((1u << lane) - 1u));
-      const int w = __popc(m);
       int incl = w;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
@@ -228,7 +240,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const int target = static_cast<int>(cum_w[s + 1]) - kWSlots;
     int f = -1;
     if (target > 0) {
-      int lo = 0, hi = s;  // cum_w[s] >= target because a step holds at most 2 NP <= kWSlots blocks
+      int lo = 0, hi = s;  // cum_w[s] >= target because a step holds at most kG NP <= kWSlots blocks
       while (lo < hi) {
         const int mid = (lo + hi) >> 1;
         if (static_cast<int>(cum_w[mid]) >= target) hi = mid; else lo = mid + 1;
@@ -237,7 +249,10 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
     wait_for[s] = static_cast<int16_t>(f);
     const int kp = step_kp[s];
-    rec[s] = kmask[2 * kp] | (kmask[2 * kp + 1] << NP) | (static_cast<uint32_t>(cum_w[s] % kWSlots) << 24);
+    uint64_t rr = static_cast<uint64_t>(cum_w[s] % kWSlots) << 48;
+#pragma unroll
+    for (int j = 0; j < kG; ++j) rr |= static_cast<uint64_t>(kmask[kG * kp + j]) << (NP * j);
+    rec[s] = rr;
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -246,19 +261,25 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const uint32_t a_tmem = tmem_base + kAccCols;  // activation ring
 
   bool failed = false;  // a bounded wait of this thread gave up
-  if (warp >= kProd0 && warp < kMma0) {
+  if (warp >= kProd0) {
     // ------------------------------ producers ------------------------------
-    // lanes 0 .. NP-1 fetch the W blocks of the pair's first K-block, lanes 16 .. 16+NP-1 those of the second
+    // W blocks: one instruction per pair of K-blocks; lanes 0 .. NP-1 fetch the blocks of the pair's
+    // first K-block, lanes 16 .. 16+NP-1 those of the second
     const long long wrow0 = ((long long)batch * p.val_stride_blocks + e0) * kBlk;  // row in the [blocks * 32, 32] view
     const int half = lane >> 4, l = lane & 15;
     bool ok = true;
     for (int s = warp - kProd0; s < n_steps; s += kProdWarps) {
       const int kp = step_kp[s];
-      const uint32_t r = rec[s];
-      const uint32_t pack = (r & kLow) | (((r >> NP) & kLow) << 16);  // one bit per lane that has a block to fetch
-      const int c0 = (r >> 24) & 0x3f, wf = wait_for[s];
-      const bool have = (pack >> lane) & 1u;
-      const int src = have ? wsrc[(2 * kp + half) * NP + l] : 0;
+      const uint64_t r = rec[s];
+      const int c0 = static_cast<int>(r >> 48) & 0x3f, wf = wait_for[s];
+      uint32_t pack[kSubTiles];  // per pair of K-blocks: one bit per lane that has a block to fetch
+      int src[kSubTiles], n_blocks = 0;
+#pragma unroll
+      for (int t = 0; t < kSubTiles; ++t) {
+        pack[t] = (static_cast<uint32_t>(r >> (2 * t * NP)) & kLow) | ((static_cast<uint32_t>(r >> ((2 * t + 1) * NP)) & kLow) << 16);
+        src[t] = ((pack[t] >> lane) & 1u) ? wsrc[(kG * kp + 2 * t + half) * NP + l] : 0;
+        n_blocks += __popc(pack[t]);
+      }
       // An mbarrier wait names a phase by its parity only, so a waiter must know that the barrier is
       // at most one phase away from the one it names.  Releases are monotonic and this warp's previous
       // step (s - kProdWarps) confirmed the release of step s - kProdWarps - kXSlots, the predecessor of
@@ -268,14 +289,22 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       if (wf >= 0 && wf > s - kXSlots && !mbar_wait_warp(&empty_bar[wf % kXSlots], (wf / kXSlots) & 1)) { ok = false; break; }
       const int slot = s % kXSlots;
       if (lane == 0) {
-        mbar_arrive_expect_tx(&full_bar[slot], kXBytes + __popc(pack) * kWBytes);
-        tma_load_2d(x_ring + slot * kXBytes, &tm_x, kp * kStepK, batch * p.M + m0, &full_bar[slot]);
+        mbar_arrive_expect_tx(&full_bar[slot], kXBytes + n_blocks * kWBytes);
+#pragma unroll
+        for (int t = 0; t < kSubTiles; ++t)
+          tma_load_2d(x_ring + slot * kXBytes + t * kSubBytes, &tm_x, kp * kStepK + t * kSubK, batch * p.M + m0,
+                      &full_bar[slot]);
       }
       __syncwarp();  // the expected byte count is registered before any lane's load can complete
-      if (have) {
-        int ws = c0 + __popc(pack & ((1u << lane) - 1u));  // rank among the step's blocks
-        if (ws >= kWSlots) ws -= kWSlots;
-        tma_load_2d(w_ring + ws * kWBytes, &tm_w, 0, (int)(wrow0 + (long long)src * kBlk), &full_bar[slot]);
+      int before = c0;  // ring position of the pair's first block
+#pragma unroll
+      for (int t = 0; t < kSubTiles; ++t) {
+        if ((pack[t] >> lane) & 1u) {
+          int ws = before + __popc(pack[t] & ((1u << lane) - 1u));  // rank among the step's blocks
+          if (ws >= kWSlots) ws -= kWSlots;
+          tma_load_2d(w_ring + ws * kWBytes, &tm_w, 0, (int)(wrow0 + (long long)src[t] * kBlk), &full_bar[slot]);
+        }
+        before += __popc(pack[t]);
       }
       __syncwarp();
     }
@@ -291,9 +320,9 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const uint32_t mine = kMineBase << (warp - kMma0);  // accumulators issued by this warp
     uint32_t written = 0;
     bool ok = true;
-    uint32_t r_next = n_steps > 0 ? rec[0] : 0u;
+    uint64_t r_next = n_steps > 0 ? rec[0] : 0ull;
     for (int s = 0; s < n_steps; ++s) {
-      const uint32_t r = r_next;
+      const uint64_t r = r_next;
       if (s + 1 < n_steps) r_next = rec[s + 1];  // fetched ahead of the wait
       const int slot = s % kXSlots, aslot = s & (kASlots - 1);
       // Every issuer waits for the activations of every step and commits to its "empty" barrier, also
@@ -303,30 +332,35 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       // which is what the producers' wait_for table assumes.  The step's "full" phase completed before
       // its converters ran, so the W blocks are in place too.
       if (!mbar_wait(&afull_bar[aslot], (s / kASlots) & 1)) { ok = false; break; }
-      const uint32_t mk[2] = {r & kLow, (r >> NP) & kLow};
-      if (((mk[0] | mk[1]) & mine) == 0u) {
+      uint32_t mk[kG], any = 0u;
+#pragma unroll
+      for (int j = 0; j < kG; ++j) {
+        mk[j] = static_cast<uint32_t>(r >> (NP * j)) & kLow;
+        any |= mk[j];
+      }
+      if ((any & mine) == 0u) {
         if (leader) umma_commit(&empty_bar[slot]);
         continue;
       }
       tc_fence_after_sync();
-      const uint32_t c0 = (r >> 24) & 0x3fu;
-      const uint32_t n_first = __popc(mk[0]);  // the ring holds the first K-block's W blocks, then the second's
+      uint32_t before = static_cast<uint32_t>(r >> 48) & 0x3fu;  // ring position of the K-block's first W block
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
+      for (int j = 0; j < kG; ++j) {
         uint32_t m = mk[j] & mine;
-        const uint32_t a_addr = a_tmem + aslot * kACols + j * (kACols / 2);
+        const uint32_t a_addr = a_tmem + aslot * kACols + j * (kBlk / 2);
         while (m) {
           const int l = __ffs(m) - 1;
           m &= m - 1;
-          uint32_t w = c0 + (j ? n_first : 0u) + __popc(mk[j] & ((1u << l) - 1u));  // rank among the step's blocks
+          uint32_t w = before + __popc(mk[j] & ((1u << l) - 1u));  // rank among the step's blocks
           if (w >= kWSlots) w -= kWSlots;
           const uint32_t b_lo = (w_base + w * kWBytes) >> 4;
           if (leader) {
             umma_ts(tmem_base + l * kBlk, a_addr, desc_hi | b_lo, idesc, (written >> l) & 1u);
-            umma_ts(tmem_base + l * kBlk, a_addr + kACols / 4, desc_hi | (b_lo + 2), idesc, 1u);
+            umma_ts(tmem_base + l * kBlk, a_addr + kBlk / 4, desc_hi | (b_lo + 2), idesc, 1u);
           }
           written |= 1u << l;
         }
+        before += __popc(mk[j]);
       }
       if (leader) umma_commit(&empty_bar[slot]);  // frees the step's X tile, W blocks and activation slot
     }
@@ -347,14 +381,17 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       // release of step s - kConvSets - kASlots on its previous turn, so the parity cannot alias)
       if (s >= kASlots && !mbar_wait_warp(&empty_bar[(s - kASlots) % kXSlots], ((s - kASlots) / kXSlots) & 1)) { ok = false; break; }
       if (!mbar_wait_warp(&full_bar[slot], (s / kXSlots) & 1)) { ok = false; break; }
-      const uint8_t* xrow = x_ring + slot * kXBytes + row * (kStepK * 2);
-      uint32_t r[32];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((c ^ sw) << 4));
-        r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
+      for (int t = 0; t < kSubTiles; ++t) {
+        const uint8_t* xrow = x_ring + slot * kXBytes + t * kSubBytes + row * (kSubK * 2);
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((c ^ sw) << 4));
+          r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
+        }
+        tmem_st_x32(a_tmem + aslot * kACols + t * (kSubK / 2) + lane_addr, r);
       }
-      tmem_st_x32(a_tmem + aslot * kACols + lane_addr, r);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
@@ -399,7 +436,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           }
         }
         // tile l / 2, row `row`, 16-byte chunks (l % 2) * 4 .. + 3, each at chunk position c ^ (row & 7)
-        uint8_t* trow = x_ring + (l >> 1) * kXBytes + row * 128;
+        uint8_t* trow = x_ring + (l >> 1) * kSubBytes + row * 128;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const uint32_t c = static_cast<uint32_t>((l & 1) * 4 + j) ^ sw;
@@ -413,7 +450,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     if (warp == 0 && lane == 0 && !failed) {
       const int n_tiles = (nb_end - nb0 + 1) / 2;
       for (int t = 0; t < n_tiles; ++t)
-        tma_store_2d(&tm_c, x_ring + t * kXBytes, (nb0 + 2 * t) * kBlk, batch * p.M + m0);
+        tma_store_2d(&tm_c, x_ring + t * kSubBytes, (nb0 + 2 * t) * kBlk, batch * p.M + m0);
       tma_store_commit_and_wait();
     }
   }
@@ -431,7 +468,7 @@ int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
   {
     const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.batch * p.M};
     const uint64_t strides[1] = {(uint64_t)p.K * 2};
-    const uint32_t box[2] = {kStepK, kTileM};
+    const uint32_t box[2] = {kSubK, kTileM};
     int rc = make_tensor_map(&tm_x, p.A, p.dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != SPARTA_OK) return rc;
   }
@@ -446,7 +483,7 @@ int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
   {
     const uint64_t dims[2] = {(uint64_t)p.N, (uint64_t)p.batch * p.M};
     const uint64_t strides[1] = {(uint64_t)p.N * 2};
-    const uint32_t box[2] = {kStepK, kTileM};
+    const uint32_t box[2] = {kSubK, kTileM};
     int rc = make_tensor_map(&tm_c, p.C, p.dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != SPARTA_OK) return rc;
   }
