@@ -15,30 +15,32 @@
 // 128 x 32 in tensor memory (384 columns), plus a ring of kASlots = 4 activation tiles (128 lanes x 32
 // columns each) in the remaining 128 columns.  The shared-memory rings that TMA fills run deeper
 // (kXSlots = 6 steps), because a step's loads take far longer to arrive than its MMAs take to run.
-// A "step" is an aligned pair of K-blocks (64 values of K) of which at least one is kept by a
+// A "step" is an aligned group of kG = 2 K-blocks (64 values of K) of which at least one is kept by a
 // row-block of the panel: 128-byte rows are the widest a swizzled TMA box can fetch, and a bulk tensor
 // load costs the TMA unit about 1.3-1.9 cycles per box row however wide the row is, so fetching the
-// activations in 64-byte rows would cost twice as much per K-block.  The prologue turns the BCSR
-// rows of the panel into a complete schedule in shared memory -- per step its K-block, the W blocks
-// it needs (kmask of its two K-blocks), where each of them sits in the value array (wsrc), its position in the W ring
-// (cum_w) and the earlier step whose release makes room for it (wait_for) -- so the roles below run
-// without per-step messages and with almost no bookkeeping of their own; a single warp executes
-// dependent instructions at only one per ~5 cycles, which made run-time bookkeeping the bottleneck.
-//   warps 4-7    producers: warp j issues the TMA loads of steps j, j + 4, ... (X tile by coordinate,
+// activations in 64-byte rows would cost twice as much per K-block.  (kG = 4, two such boxes per step
+// and half as many steps, measured the same.)  The prologue turns the BCSR rows of the panel into a
+// complete schedule in shared memory -- per step its K-group, the W blocks it needs (kmask of its
+// K-blocks), where each of them sits in the value array (wsrc), its position in the W ring (cum_w)
+// and the latest earlier step whose W blocks still occupy that ring space (wait_for) -- so the roles
+// below run without per-step messages and with almost no bookkeeping of their own; a single warp
+// executes dependent instructions at only one per ~5 cycles, which made run-time bookkeeping the
+// bottleneck of an earlier version.
+//   warps 20-23  producers: warp j issues the TMA loads of steps j, j + 4, ... (X tile by coordinate,
 //                W blocks gathered by BCSR position, one per lane in a single instruction; all complete
 //                on the step's "full" mbarrier).  Issuing one bulk tensor load costs the issuing warp
 //                50-140 cycles, hence four warps.
 //   warps 0-3,   converters: shared memory -> registers -> tcgen05.st into the step's slot of the
-//   12-15        activation ring (each warp its own 32-lane quadrant; the two sets alternate steps),
+//   16-19        activation ring (each warp its own 32-lane quadrant; the two sets alternate steps),
 //                then arrive on the step's "a_full" mbarrier
-//   warps 8-11   MMA issue: each warp owns the accumulators l with l % 4 == its index and one of its
-//                threads issues tcgen05.mma with A from tensor memory (two K = 16 slabs per W block).
-//                A wait, a commit and an MMA each cost the issuing thread 80-100 cycles, which is why
-//                a step spans two K-blocks and why every issuer thread counts;
-//                tcgen05.commit arrives on the step's "empty" mbarrier, which frees the X tile, the W
-//                blocks and the activation slot once all four have arrived.  One thread sustains about
-//                one MMA per 45 cycles, hence four issuers.
-//   warps 0-3, 12-15 afterwards: epilogue, tcgen05.ld -> + bias -> fp16 / bf16 -> shared memory -> TMA store
+//   warps 4-15   MMA issue: warp 4 + l owns accumulator l, and one of its threads issues tcgen05.mma
+//                with A from tensor memory (two K = 16 slabs per W block); MMAs into one accumulator
+//                must come from one thread to stay ordered.  A wait, a commit and an MMA each cost the
+//                issuing thread 80-100 cycles, so every issuer thread counts.  Every issuer commits to
+//                the "empty" mbarrier of every step (also of steps in which it has no block), which
+//                frees the X tile, the W blocks and the activation slot once all twelve have arrived
+//                and makes releases monotonic.
+//   warps 0-3, 16-19 afterwards: epilogue, tcgen05.ld -> + bias -> fp16 / bf16 -> shared memory -> TMA store
 // Every mbarrier wait is bounded; a wait that runs out sets a status word and the CTA winds down.
 //
 // Replaces sparta_sparse_matmul_dsd.cuh.j2 / openai_sparse_matmul_dsd.cuh.j2 for this layout.

@@ -29,6 +29,8 @@ def _dsd_case(batch, M, K, N, sparsity, dtype, biased, seed, empty_rows=()):
     (2, 256, 256, 192, 0.5),    # partial panel (6 block columns), batch
     (1, 512, 1024, 1024, 0.9),  # several panels, sparse rows
     (1, 384, 2048, 544, 0.75),  # 17 block columns: a full and a one-column panel
+    (1, 128, 96, 416, 0.5),     # odd number of K blocks (a half-empty last step), 13 block columns
+    (3, 256, 4096, 384, 0.97),  # long K, most steps empty: the rings wrap many times with few blocks
 ])
 def test_dsd_tcgen05(dtype, biased, batch, M, K, N, sparsity):
     x, w, b, mask = _dsd_case(batch, M, K, N, sparsity, dtype, biased, seed=M + K + N,
