@@ -76,7 +76,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 16; ++i)
-      if (mbar_try_wait_suspend(bar, parity, 4000u)) return true; else __nanosleep(100);
+      if (mbar_try_wait_suspend(bar, parity, 4000u)) return true;
     if (global_timer_ns() - t0 > kWaitNanos) return false;
   }
 }
