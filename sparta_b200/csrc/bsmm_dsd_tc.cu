@@ -64,23 +64,28 @@ constexpr int kStepK = kG * kBlk;   // K values per step
 constexpr int kXBytes = kSubTiles * kSubBytes;
 constexpr int kWBytes = kBlk * kBlk * 2;      // 2 KB
 constexpr int kACols = kStepK / 2;  // tensor-memory columns of one activation tile (two 16-bit values per column)
-constexpr int kNP = 12;             // block columns per CTA
+constexpr int kNPMax = 12;          // block columns per CTA: 8, 10 or 12, chosen per launch (template parameter NP)
 constexpr int kMaxKb = kG == 2 ? 1024 : 512;  // K-blocks the schedule can hold (K <= 32768 or 16384): shared-memory budget
 constexpr int kMaxSteps = kMaxKb / kG;
 constexpr int kXSlots = 12 / kG;    // steps whose loads (X tile, W blocks) are in flight: 96 KB of X
-constexpr int kASlots = 8 / kG;     // steps whose activations sit in tensor memory (128 columns); a power of two
+// steps whose activations sit in tensor memory: the tiles that fit beside the NP accumulators, an even
+// number (each slot must always belong to the same converter set), at most kXSlots
+constexpr int a_slots(int np) {
+  const int fit = ((512 - np * kBlk) / (kG * kBlk / 2)) & ~1;
+  return fit < kXSlots ? fit : (kXSlots & ~1);
+}
 constexpr int kWSlots = kG == 2 ? 40 : 48;    // W blocks in flight
-constexpr int kMmaWarps = 12;       // MMA-issuing warps: one per accumulator
+constexpr int kMmaWarps = 12;       // warps reserved for MMA issue (a multiple of 4); the first NP are used, one per accumulator
 constexpr int kConvSets = 2;        // converter warp sets (four warps each) that alternate steps
 constexpr int kProdWarps = kXSlots < 4 ? kXSlots : 4;  // TMA-issuing warps; at most kXSlots (see the producers' wait)
 constexpr int kMma0 = 4;            // first MMA-issuing warp
 constexpr int kConv1 = kMma0 + kMmaWarps;    // first warp of the second converter set (a multiple of 4)
 constexpr int kProd0 = kConv1 + 4;  // first producer warp
 constexpr int kThreads = 32 * (kProd0 + kProdWarps);
-static_assert(kProdWarps <= kXSlots && kASlots <= kXSlots, "a producer may run at most one ring turn ahead of the release it waits for");
+static_assert(kProdWarps <= kXSlots, "a producer may run at most one ring turn ahead of the release it waits for");
 static_assert(kConv1 % 4 == 0, "converter warps must map onto their tensor-memory lane quadrant");
-static_assert(kNP <= 12 && kNP % kMmaWarps == 0, "a step record packs two 12-bit block masks");
-static_assert(kWSlots >= kG * kNP && kWSlots < 64, "a step's W blocks must fit the ring; its position packs into 6 bits");
+static_assert(kNPMax <= 12 && kNPMax <= kMmaWarps, "a step record packs 12-bit block masks; one issuer warp per accumulator");
+static_assert(kWSlots >= kG * kNPMax && kWSlots < 64, "a step's W blocks must fit the ring; its position packs into 6 bits");
 
 struct DsdTcParams {
   const int32_t* row_ptr;
@@ -92,40 +97,34 @@ struct DsdTcParams {
   int32_t* status;
 };
 
-constexpr uint32_t kAccCols = kNP * kBlk;   // 384
 constexpr uint32_t kTmemCols = 512;
-static_assert(kAccCols + kASlots * kACols <= kTmemCols, "tensor memory budget");
-static_assert(kXSlots * kXBytes >= (kNP / 2) * kSubBytes, "the epilogue stages the output tile in the X ring");
+static_assert(kXSlots * kXBytes >= (kNPMax / 2) * kSubBytes, "the epilogue stages the output tile in the X ring");
 
 // shared-memory carve-up (byte offsets from a 1 KB aligned base)
 constexpr int kOffX = 0;                                  // X ring   [kXSlots][128 rows x 128 B]
 constexpr int kOffW = kOffX + kXSlots * kXBytes;           // W ring   [kWSlots][2 KB]
 constexpr int kOffMask = kOffW + kWSlots * kWBytes;       // kmask    [Kb]        u32: row-blocks keeping K-block k
-constexpr int kOffSrc = kOffMask + kMaxKb * 4;            // wsrc     [Kb][kNP]   u16: BCSR position within the panel
-constexpr int kOffStep = kOffSrc + kMaxKb * kNP * 2;      // step_kp  [steps]     u16: K-pair index
+constexpr int kOffSrc = kOffMask + kMaxKb * 4;            // wsrc     [Kb][NP]    u16: BCSR position within the panel
+constexpr int kOffStep = kOffSrc + kMaxKb * kNPMax * 2;      // step_kp  [steps]     u16: K-pair index
 constexpr int kOffCum = kOffStep + kMaxSteps * 2;         // cum_w    [steps + 1] u16: W blocks of all earlier steps
 constexpr int kOffWait = kOffCum + (kMaxSteps + 8) * 2;   // wait_for [steps]     s16
 constexpr int kOffRec = (kOffWait + kMaxSteps * 2 + 7) / 8 * 8;  // rec [steps] u64: 12-bit block mask per K-block | ring pos << 48
-constexpr int kOffBias = kOffRec + kMaxSteps * 8;         // bias     [kNP * 32]  f32
-constexpr int kOffCtl = kOffBias + kNP * kBlk * 4;        // mbarriers and scalars
+constexpr int kOffBias = kOffRec + kMaxSteps * 8;         // bias     [NP * 32]   f32
+constexpr int kOffCtl = kOffBias + kNPMax * kBlk * 4;        // mbarriers and scalars
 constexpr int kSmemTotal = kOffCtl + 512 + 1024 /* alignment slack */;
 static_assert(kOffRec % 8 == 0 && kOffBias % 8 == 0 && kOffCtl % 8 == 0, "alignment of the shared-memory tables");
 static_assert(kSmemTotal <= 227 * 1024, "shared memory budget");
 
-constexpr uint32_t mine_mask(int np, int issuers) {
-  uint32_t m = 0;
-  for (int l = 0; l < np; l += issuers) m |= 1u << l;
-  return m;
-}
-
-template <int FMT>
+template <int FMT, int NP>
 __global__ void __launch_bounds__(kThreads, 1)
 bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    const __grid_constant__ CUtensorMap tm_c, DsdTcParams p) {
   using T = typename std::conditional<FMT == 0, __half, __nv_bfloat16>::type;
-  constexpr int NP = kNP;
-  constexpr int kIssuers = kMmaWarps;
-  constexpr uint32_t kMineBase = mine_mask(NP, kMmaWarps);  // accumulators l with l % kIssuers == 0
+  static_assert(NP % 2 == 0 && NP <= kNPMax, "panel width");
+  constexpr int kASlots = a_slots(NP);
+  constexpr uint32_t kAccCols = NP * kBlk;
+  static_assert(kASlots >= 2 && kAccCols + kASlots * kACols <= kTmemCols, "tensor memory budget");
+  constexpr int kIssuers = NP;  // issuer warps in use
   constexpr uint32_t kLow = (1u << NP) - 1u;
 
   extern __shared__ uint8_t smem_raw[];
@@ -312,21 +311,21 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
     failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[0], 1);
-  } else if (warp >= kMma0 && warp < kConv1) {
+  } else if (warp >= kMma0 && warp < kMma0 + kIssuers) {  // (warps up to kConv1 are spare when NP < 12)
     // ------------------------------ MMA issue ------------------------------
     // Operand addresses derive from the schedule only, so they stay warp-uniform; one lane issues.
     constexpr uint32_t idesc = make_idesc_f16(kTileM, kBlk, FMT, 0, 0);
     const uint32_t w_base = smem_u32(w_ring);
     const uint64_t desc_hi = make_smem_desc(0, 16, 512, SW_64B);
     const bool leader = lane == 0;
-    const uint32_t mine = kMineBase << (warp - kMma0);  // accumulators issued by this warp
+    const uint32_t mine = 1u << (warp - kMma0);  // the accumulator issued by this warp
     uint32_t written = 0;
     bool ok = true;
     uint64_t r_next = n_steps > 0 ? rec[0] : 0ull;
     for (int s = 0; s < n_steps; ++s) {
       const uint64_t r = r_next;
       if (s + 1 < n_steps) r_next = rec[s + 1];  // fetched ahead of the wait
-      const int slot = s % kXSlots, aslot = s & (kASlots - 1);
+      const int slot = s % kXSlots, aslot = s % kASlots;
       // Every issuer waits for the activations of every step and commits to its "empty" barrier, also
       // in a step in which it has no block.  The wait keeps it within one ring turn of the converters,
       // so a phase parity is never mistaken for an older one; the commit makes the release of steps
@@ -378,7 +377,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     bool ok = true;
     for (int s = conv_set; s < n_steps; s += kConvSets) {
-      const int slot = s % kXSlots, aslot = s & (kASlots - 1);
+      const int slot = s % kXSlots, aslot = s % kASlots;
       // the activation slot is free once the MMAs of step s - kASlots are done (this warp confirmed the
       // release of step s - kConvSets - kASlots on its previous turn, so the parity cannot alias)
       if (s >= kASlots && !mbar_wait_warp(&empty_bar[(s - kASlots) % kXSlots], ((s - kASlots) / kXSlots) & 1)) { ok = false; break; }
@@ -464,7 +463,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   }
 }
 
-template <int FMT>
+template <int FMT, int NP>
 int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
   CUtensorMap tm_x, tm_w;
   {
@@ -498,14 +497,14 @@ int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
   q.val_stride_blocks = p.val_stride_blocks;
   q.status = device_status_ptr();
   if (!q.status) return SPARTA_ERR_DRIVER;
-  auto kern = bsmm_dsd_tc_kernel<FMT>;
+  auto kern = bsmm_dsd_tc_kernel<FMT, NP>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
-  dim3 grid((q.Nb + kNP - 1) / kNP, p.M / kTileM, p.batch);
+  dim3 grid((q.Nb + NP - 1) / NP, p.M / kTileM, p.batch);
   kern<<<grid, kThreads, kSmemTotal, st>>>(tm_x, tm_w, tm_c, q);
   return launch_status();
 }
@@ -526,7 +525,24 @@ bool dsd_tc_supported(const BsmmParams& p) {
 }
 
 int dsd_tc_launch(const BsmmParams& p, cudaStream_t st) {
-  return p.dtype == SPARTA_F16 ? launch_dsd_tc<0>(p, st) : launch_dsd_tc<1>(p, st);
+  // Panel width: narrower panels leave more tensor memory for activation tiles in flight and give more
+  // CTAs, wider ones re-read the activations less.  Cost model: waves of CTAs x (a fixed part per CTA
+  // + the panel's share of the blocks), fitted to the 4096^3 measurements (10 columns beat 12 by 4 %, 8
+  // lost 17 %).
+  const long long tiles = (long long)(p.M / kTileM) * p.batch;
+  int best = 12;
+  long long best_cost = -1;
+  for (int np : {12, 10, 8}) {
+    const long long ctas = (long long)((p.N / kBlk + np - 1) / np) * tiles;
+    const long long cost = ((ctas + kNumSMs - 1) / kNumSMs) * (6 + np);
+    if (best_cost < 0 || cost < best_cost) { best = np; best_cost = cost; }
+  }
+  const bool h = p.dtype == SPARTA_F16;
+  switch (best) {
+    case 8: return h ? launch_dsd_tc<0, 8>(p, st) : launch_dsd_tc<1, 8>(p, st);
+    case 10: return h ? launch_dsd_tc<0, 10>(p, st) : launch_dsd_tc<1, 10>(p, st);
+    default: return h ? launch_dsd_tc<0, 12>(p, st) : launch_dsd_tc<1, 12>(p, st);
+  }
 }
 
 }  // namespace sparta

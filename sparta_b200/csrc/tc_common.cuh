@@ -69,9 +69,13 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t pa
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the phase did not complete within kWaitNanos.
+// Bounded wait: false when the phase did not complete within kWaitNanos.  The clock is only read
+// after a few hundred polls: reading %globaltimer on the way into every wait that does not succeed at
+// once put a fixed cost on each hand-off between warps, which is the critical path of the pipelines.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (int i = 0; i < 256; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   while (true) {
 #pragma unroll 1

@@ -1,6 +1,6 @@
 """Discrete-event simulation of the mbarrier protocol of the tcgen05 dsd kernel
 (``sparta_b200/csrc/bsmm_dsd_tc.cu``): four producer warps, two converter sets, twelve issuers, rings
-of 6 load slots / 4 activation slots / 40 W blocks, waits that name a phase by its parity only.
+of 6 load slots / 4 or 6 activation slots / 40 W blocks, waits that name a phase by its parity only.
 
 The simulation runs the roles' wait / arrive sequences under random timing with the mbarrier rules
 (a wait for parity P succeeds when the barrier's current phase has the other parity; an arrival beyond
@@ -14,7 +14,7 @@ import random
 import numpy as np
 import pytest
 
-NP, KX, KA, KW, NPROD, NISS = 12, 6, 4, 40, 4, 12
+NP, KX, KW, NPROD = 12, 6, 40, 4
 
 
 class Barrier:
@@ -45,7 +45,9 @@ def wait_for_table(need):
     return cum, table
 
 
-def simulate(need, seed):
+def simulate(need, seed, KA=4, NISS=12):
+    """KA activation slots in tensor memory, NISS issuer warps (4 / 12 for panels of 12 block columns,
+    6 / 10 for panels of 10, 6 / 8 for panels of 8)."""
     rnd = random.Random(seed)
     n = len(need)
     cum, wait_for = wait_for_table(need)
@@ -135,12 +137,13 @@ def simulate(need, seed):
     assert not w_owner and all(o is None for o in x_owner) and all(o is None for o in a_owner)
 
 
+@pytest.mark.parametrize('ka,niss', [(4, 12), (6, 10), (6, 8)])
 @pytest.mark.parametrize('density', [0.02, 0.1, 0.25, 0.5, 1.0])
-def test_protocol_under_random_timing(density):
-    rs = np.random.RandomState(int(density * 1000))
-    for trial in range(12):
-        need = np.maximum(1, rs.binomial(2 * NP, density, size=rs.randint(1, 100)))
-        simulate(need, seed=trial)
+def test_protocol_under_random_timing(density, ka, niss):
+    rs = np.random.RandomState(int(density * 1000) + ka)
+    for trial in range(8):
+        need = np.maximum(1, rs.binomial(2 * niss, density, size=rs.randint(1, 100)))
+        simulate(need, seed=trial, KA=ka, NISS=niss)
 
 
 def test_wait_for_table_small_case():
