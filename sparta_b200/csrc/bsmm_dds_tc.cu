@@ -50,7 +50,7 @@ struct DdsTcParams {
   int32_t* status;
 };
 
-template <int FMT, int STAGES>
+template <int FMT, int STAGES, bool LOOP>
 __global__ void __launch_bounds__(kThreads, STAGES == 2 ? 2 : 1)
 bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    DdsTcParams p) {
@@ -82,7 +82,6 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     s_range[1] = row_ptr[mb0 + 4];
   }
   for (int c = threadIdx.x; c < p.Nb; c += kThreads) cmask[c] = 0;
-  for (int i = threadIdx.x; i < 4 * kGroup; i += kThreads) s_pos[i] = -1;
   __syncthreads();
   for (int e = s_range[0] + threadIdx.x; e < s_range[1]; e += kThreads) {
     const int v = __ldg(idx + e);
@@ -103,16 +102,7 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   }
   __syncthreads();
   const int ncols_total = *s_count;
-  const int c_first = group * kGroup;
-  if (c_first >= ncols_total) return;  // nothing for this group: leave before any barrier / TMEM use
-  const int ncols = min(kGroup, ncols_total - c_first);
-  // BCSR positions of the kept blocks of this group (for the compressed output)
-  for (int e = s_range[0] + threadIdx.x; e < s_range[1]; e += kThreads) {
-    const int v = __ldg(idx + e);
-    const int c = v & 0xffff;
-    for (int l = 0; l < ncols; ++l)
-      if (clist[c_first + l] == c) s_pos[((v >> 16) - mb0) * kGroup + l] = e;
-  }
+  if (group * kGroup >= ncols_total) return;  // nothing for this CTA: leave before any barrier / TMEM use
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -132,14 +122,22 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   const uint32_t tmem_base = *tmem_holder;
   const int nchunks = p.K / kChunkK;
 
+  // A CTA takes the groups blockIdx.x, blockIdx.x + gridDim.x, ... of its row tile one after the other:
+  // the union of needed columns, the barriers and the tensor memory are set up once.  The pipeline
+  // barriers keep their phases across groups (cc counts chunks since the start); a CTA-wide barrier
+  // separates the groups, so the accumulator and s_pos are free when the next group starts.
   bool failed = false;  // a bounded wait of this thread gave up
+  int cc0 = 0;          // chunks issued by the groups before this one
+  for (int it = 0, g = group; g * kGroup < ncols_total; g += gridDim.x, ++it, cc0 += nchunks) {
+  const int c_first = g * kGroup;
+  const int ncols = min(kGroup, ncols_total - c_first);
   if (warp == 4) {
     // ------------------------------ producer ------------------------------
     const int col = lane < ncols ? clist[c_first + lane] : 0;
     bool ok = true;
     for (int c = 0; c < nchunks; ++c) {
-      const int s = c % STAGES;
-      if (!mbar_wait(&empty_bar[s], ((c / STAGES) & 1) ^ 1)) { ok = false; break; }
+      const int cc = LOOP ? cc0 + c : c, s = cc % STAGES;
+      if (!mbar_wait(&empty_bar[s], ((cc / STAGES) & 1) ^ 1)) { ok = false; break; }
       uint8_t* st = stages + s * kStageBytes;
       if (lane == 0) {
         mbar_arrive_expect_tx(&full_bar[s], kABytes + ncols * kBBlockBytes);
@@ -165,8 +163,8 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     const uint32_t base = smem_u32(stages) >> 4;
     bool ok = true;
     for (int c = 0; c < nchunks; ++c) {
-      const int s = c % STAGES;
-      if (!mbar_wait(&full_bar[s], (c / STAGES) & 1)) { ok = false; break; }
+      const int cc = LOOP ? cc0 + c : c, s = cc % STAGES;
+      if (!mbar_wait(&full_bar[s], (cc / STAGES) & 1)) { ok = false; break; }
       tc_fence_after_sync();
       if (lane == 0) {
         const uint32_t a_lo = base + ((s * kStageBytes) >> 4);
@@ -183,7 +181,18 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     if (lane == 0) umma_commit(accum_bar);
   } else {
     // ------------------------------ epilogue: kept blocks only ------------------------------
-    if (!mbar_wait_warp(accum_bar, 0)) {
+    // BCSR positions of the kept blocks of this group (for the compressed output), found by the four
+    // epilogue warps while the loads and MMAs of the group run
+    for (int i = threadIdx.x; i < 4 * kGroup; i += 128) s_pos[i] = -1;
+    named_barrier_sync(1, 128);
+    for (int e = s_range[0] + threadIdx.x; e < s_range[1]; e += 128) {
+      const int v = __ldg(idx + e);
+      const int c = v & 0xffff;
+      for (int l = 0; l < ncols; ++l)
+        if (clist[c_first + l] == c) s_pos[((v >> 16) - mb0) * kGroup + l] = e;
+    }
+    named_barrier_sync(1, 128);
+    if (!mbar_wait_warp(accum_bar, LOOP ? (it & 1) : 0)) {
       failed = true;
       if (lane == 0) atomicExch(&p.status[2], 1);
     } else {
@@ -225,6 +234,11 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       }
     }
   }
+  if constexpr (!LOOP) break;  // launched with one CTA per group
+  tc_fence_before_sync();
+  if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }  // a wait gave up somewhere: stop here
+  tc_fence_after_sync();
+  }  // groups
   tc_fence_before_sync();
   sync_and_drain(failed);
   if (warp == 5) {
@@ -267,16 +281,32 @@ int launch_dds(const BsmmParams& p, cudaStream_t st) {
   q.ptr_stride = p.ptr_stride; q.idx_stride = p.idx_stride; q.val_stride_blocks = p.val_stride_blocks;
   q.status = device_status_ptr();
   if (!q.status) return SPARTA_ERR_DRIVER;
-  auto kern = bsmm_dds_tc_kernel<FMT, STAGES>;
   constexpr int kSmem = smem_bytes(STAGES);
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    cudaError_t e = cudaFuncSetAttribute(bsmm_dds_tc_kernel<FMT, STAGES, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(bsmm_dds_tc_kernel<FMT, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kSmem);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
-  dim3 grid((q.Nb + kGroup - 1) / kGroup, p.M / kTileM, p.batch);
-  kern<<<grid, kThreads, kSmem, st>>>(tm_a, tm_b, q);
+  // CTAs per row tile: every group its own CTA when there are few row tiles; with many (batched masks)
+  // most groups of a tile are empty, and a few CTAs per tile loop over the groups instead, aiming at
+  // about two CTAs per resident slot
+  constexpr long long kCtasPerSlot = 2;
+  const int n_groups = (q.Nb + kGroup - 1) / kGroup;
+  const long long tiles = (long long)(p.M / kTileM) * p.batch;
+  long long per_tile = (kCtasPerSlot * 2 * kNumSMs + tiles - 1) / tiles;
+  if (per_tile < 1) per_tile = 1;
+  if (per_tile >= n_groups) {
+    dim3 grid(n_groups, p.M / kTileM, p.batch);
+    bsmm_dds_tc_kernel<FMT, STAGES, false><<<grid, kThreads, kSmem, st>>>(tm_a, tm_b, q);
+  } else {
+    dim3 grid((unsigned)per_tile, p.M / kTileM, p.batch);
+    bsmm_dds_tc_kernel<FMT, STAGES, true><<<grid, kThreads, kSmem, st>>>(tm_a, tm_b, q);
+  }
   return launch_status();
 }
 
