@@ -109,7 +109,8 @@ constexpr int kOffStep = kOffSrc + kMaxKb * kNPMax * 2;      // step_kp  [steps]
 constexpr int kOffCum = kOffStep + kMaxSteps * 2;         // cum_w    [steps + 1] u16: W blocks of all earlier steps
 constexpr int kOffWait = kOffCum + (kMaxSteps + 8) * 2;   // wait_for [steps]     s16
 constexpr int kOffRec = (kOffWait + kMaxSteps * 2 + 7) / 8 * 8;  // rec [steps] u64: 12-bit block mask per K-block | ring pos << 48
-constexpr int kOffBias = kOffRec + kMaxSteps * 8;         // bias     [NP * 32]   f32
+constexpr int kOffIss = kOffRec + kMaxSteps * 8;          // iss_tab  [steps][NP][kG] u8: W ring slot of the block, 0xff = none
+constexpr int kOffBias = kOffIss + kMaxSteps * kNPMax * kG;  // bias     [NP * 32]   f32
 constexpr int kOffCtl = kOffBias + kNPMax * kBlk * 4;        // mbarriers and scalars
 constexpr int kSmemTotal = kOffCtl + 512 + 1024 /* alignment slack */;
 static_assert(kOffRec % 8 == 0 && kOffBias % 8 == 0 && kOffCtl % 8 == 0, "alignment of the shared-memory tables");
@@ -137,6 +138,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   uint16_t* cum_w = reinterpret_cast<uint16_t*>(smem + kOffCum);
   int16_t* wait_for = reinterpret_cast<int16_t*>(smem + kOffWait);
   uint64_t* rec = reinterpret_cast<uint64_t*>(smem + kOffRec);
+  uint8_t* iss_tab = smem + kOffIss;
   float* s_bias = reinterpret_cast<float*>(smem + kOffBias);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kOffCtl);  // [kXSlots] loads of a step have landed
   uint64_t* empty_bar = full_bar + kXSlots;                // [kXSlots] MMAs of a step have read their operands
@@ -254,6 +256,21 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll
     for (int j = 0; j < kG; ++j) rr |= static_cast<uint64_t>(kmask[kG * kp + j]) << (NP * j);
     rec[s] = rr;
+    // the issuers' view of the step: for every accumulator and K-block of the step, the W ring slot that
+    // holds its block (blocks take consecutive slots in K-block, then accumulator order)
+    int pos = static_cast<int>(cum_w[s] % kWSlots);
+#pragma unroll
+    for (int j = 0; j < kG; ++j) {
+      const uint32_t mk = kmask[kG * kp + j];
+      for (int l = 0; l < NP; ++l) {
+        uint8_t b = 0xff;
+        if ((mk >> l) & 1u) {
+          b = static_cast<uint8_t>(pos);
+          if (++pos == kWSlots) pos = 0;
+        }
+        iss_tab[(s * NP + l) * kG + j] = b;
+      }
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -315,55 +332,52 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     // ------------------------------ MMA issue ------------------------------
     // Operand addresses derive from the schedule only, so they stay warp-uniform; one lane issues.
     constexpr uint32_t idesc = make_idesc_f16(kTileM, kBlk, FMT, 0, 0);
-    const uint32_t w_base = smem_u32(w_ring);
+    const uint32_t w_base16 = smem_u32(w_ring) >> 4;
     const uint64_t desc_hi = make_smem_desc(0, 16, 512, SW_64B);
     const bool leader = lane == 0;
-    const uint32_t mine = 1u << (warp - kMma0);  // the accumulator issued by this warp
-    uint32_t written = 0;
+    const int l = warp - kMma0;                        // the accumulator issued by this warp
+    const uint32_t d_tmem = tmem_base + l * kBlk;
+    using Word = typename std::conditional<kG == 2, uint16_t, uint32_t>::type;  // kG bytes of the table
+    constexpr uint32_t kNone = kG == 2 ? 0xffffu : 0xffffffffu;
+    const Word* tab = reinterpret_cast<const Word*>(iss_tab) + l;
+    uint32_t slot = 0, aslot = 0, aphase = 0, accumulate = 0;
     bool ok = true;
-    uint64_t r_next = n_steps > 0 ? rec[0] : 0ull;
+    uint32_t v_next = n_steps > 0 ? tab[0] : kNone;
+    bool ready = false;  // the next step's activations were seen in place by the probe of the step before
     for (int s = 0; s < n_steps; ++s) {
-      const uint64_t r = r_next;
-      if (s + 1 < n_steps) r_next = rec[s + 1];  // fetched ahead of the wait
-      const int slot = s % kXSlots, aslot = s % kASlots;
+      const uint32_t v = v_next;
+      if (s + 1 < n_steps) v_next = tab[(s + 1) * NP];  // fetched ahead of the wait
       // Every issuer waits for the activations of every step and commits to its "empty" barrier, also
       // in a step in which it has no block.  The wait keeps it within one ring turn of the converters,
       // so a phase parity is never mistaken for an older one; the commit makes the release of steps
       // monotonic (a released step implies that every issuer's MMAs of all earlier steps are done),
       // which is what the producers' wait_for table assumes.  The step's "full" phase completed before
-      // its converters ran, so the W blocks are in place too.
-      if (!mbar_wait(&afull_bar[aslot], (s / kASlots) & 1)) { ok = false; break; }
-      uint32_t mk[kG], any = 0u;
+      // its converters ran, so the W blocks are in place too.  What to issue comes from the table the
+      // prologue built: decoding the step's masks here, on one warp, took longer than the MMAs.
+      if (!ready && !mbar_wait(&afull_bar[aslot], aphase)) { ok = false; break; }
+      if (v != kNone) {
+        tc_fence_after_sync();
+        if (leader) {
 #pragma unroll
-      for (int j = 0; j < kG; ++j) {
-        mk[j] = static_cast<uint32_t>(r >> (NP * j)) & kLow;
-        any |= mk[j];
-      }
-      if ((any & mine) == 0u) {
-        if (leader) umma_commit(&empty_bar[slot]);
-        continue;
-      }
-      tc_fence_after_sync();
-      uint32_t before = static_cast<uint32_t>(r >> 48) & 0x3fu;  // ring position of the K-block's first W block
-#pragma unroll
-      for (int j = 0; j < kG; ++j) {
-        uint32_t m = mk[j] & mine;
-        const uint32_t a_addr = a_tmem + aslot * kACols + j * (kBlk / 2);
-        while (m) {
-          const int l = __ffs(m) - 1;
-          m &= m - 1;
-          uint32_t w = before + __popc(mk[j] & ((1u << l) - 1u));  // rank among the step's blocks
-          if (w >= kWSlots) w -= kWSlots;
-          const uint32_t b_lo = (w_base + w * kWBytes) >> 4;
-          if (leader) {
-            umma_ts(tmem_base + l * kBlk, a_addr, desc_hi | b_lo, idesc, (written >> l) & 1u);
-            umma_ts(tmem_base + l * kBlk, a_addr + kBlk / 4, desc_hi | (b_lo + 2), idesc, 1u);
+          for (int j = 0; j < kG; ++j) {
+            const uint32_t b = (v >> (8 * j)) & 0xffu;
+            if (b != 0xffu) {
+              const uint32_t a_addr = a_tmem + aslot * kACols + j * (kBlk / 2);
+              const uint32_t b_lo = w_base16 + b * (kWBytes >> 4);
+              umma_ts(d_tmem, a_addr, desc_hi | b_lo, idesc, accumulate);
+              umma_ts(d_tmem, a_addr + kBlk / 4, desc_hi | (b_lo + 2), idesc, 1u);
+              accumulate = 1u;
+            }
           }
-          written |= 1u << l;
         }
-        before += __popc(mk[j]);
       }
-      if (leader) umma_commit(&empty_bar[slot]);  // frees the step's X tile, W blocks and activation slot
+      // The issuers usually run a few steps behind the converters: probe the next step's barrier now, so
+      // that the round trip of the probe overlaps the commit instead of opening the next iteration.
+      const uint32_t slot_done = slot;
+      if (++slot == kXSlots) slot = 0;
+      if (++aslot == kASlots) { aslot = 0; aphase ^= 1u; }
+      ready = s + 1 < n_steps && mbar_test_wait(&afull_bar[aslot], aphase);
+      if (leader) umma_commit(&empty_bar[slot_done]);  // frees the step's X tile, W blocks and activation slot
     }
     failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[1], 1);

@@ -55,6 +55,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking probe of a phase: never suspends the thread, so it can be issued ahead of other work and
+// its answer read later.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // try_wait that lets the hardware suspend the warp for up to `hint_ns` until the phase completes: a
 // waiting warp then issues almost nothing, instead of flooding the memory-instruction queue that TMA
 // issue, shared-memory loads and tcgen05 traffic of the working warps also go through.
@@ -73,9 +86,10 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t pa
 // after a few hundred polls: reading %globaltimer on the way into every wait that does not succeed at
 // once put a fixed cost on each hand-off between warps, which is the critical path of the pipelines.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
 #pragma unroll 1
-  for (int i = 0; i < 256; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+  for (int i = 0; i < 64; ++i)
+    if (mbar_try_wait_suspend(bar, parity, 2000u)) return true;
   const unsigned long long t0 = global_timer_ns();
   while (true) {
 #pragma unroll 1
