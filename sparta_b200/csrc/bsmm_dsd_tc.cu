@@ -11,35 +11,46 @@
 // a K-block are shared by every W block of that K-block in the CTA's panel, so they are moved into
 // tensor memory once per K-block and reused from there.
 //
-// One CTA owns 128 token rows x a panel of NP = 12 block columns, i.e. 12 fp32 accumulators of
-// 128 x 32 in tensor memory (384 columns), plus a ring of kASlots = 4 activation tiles (128 lanes x 32
-// columns each) in the remaining 128 columns.  The shared-memory rings that TMA fills run deeper
-// (kXSlots = 6 steps), because a step's loads take far longer to arrive than its MMAs take to run.
-// A "step" is an aligned group of kG = 2 K-blocks (64 values of K) of which at least one is kept by a
-// row-block of the panel: 128-byte rows are the widest a swizzled TMA box can fetch, and a bulk tensor
-// load costs the TMA unit about 1.3-1.9 cycles per box row however wide the row is, so fetching the
-// activations in 64-byte rows would cost twice as much per K-block.  (kG = 4, two such boxes per step
-// and half as many steps, measured the same.)  The prologue turns the BCSR rows of the panel into a
-// complete schedule in shared memory -- per step its K-group, the W blocks it needs (kmask of its
-// K-blocks), where each of them sits in the value array (wsrc), its position in the W ring (cum_w)
-// and the latest earlier step whose W blocks still occupy that ring space (wait_for) -- so the roles
-// below run without per-step messages and with almost no bookkeeping of their own; a single warp
-// executes dependent instructions at only one per ~5 cycles, which made run-time bookkeeping the
-// bottleneck of an earlier version.
-//   warps 20-23  producers: warp j issues the TMA loads of steps j, j + 4, ... (X tile by coordinate,
-//                W blocks gathered by BCSR position, one per lane in a single instruction; all complete
-//                on the step's "full" mbarrier).  Issuing one bulk tensor load costs the issuing warp
-//                50-140 cycles, hence four warps.
+// One CTA owns 128 token rows x a panel of NP = 8, 10 or 12 block columns, i.e. NP fp32 accumulators
+// of 128 x 32 in tensor memory, plus a ring of kASlots = 4, 3 or 2 activation tiles (128 lanes x 64
+// columns each) in the remaining columns.  A "step" is an aligned group of kG = 4 K-blocks (128 values
+// of K) of which at least one is kept by a row-block of the panel; its activations arrive as two TMA
+// boxes of 128-byte rows (the widest a swizzled box can fetch; a bulk tensor load costs the TMA unit
+// about 1.3-1.9 cycles per box row however wide the row is, so 64-byte rows would cost twice as much
+// per K-block).  What a step costs is mostly not its work: with loads, conversion and MMAs all
+// switched off the kernel still takes three quarters of its time, because every role pays 100-150
+// cycles for each mbarrier wait (also one that succeeds at once), 50-80 for a commit and 150-200 for a
+// hand-off to the next warp, per step.  Hence steps of four K-blocks rather than two (22 % faster at
+// 75 % sparsity, 5 % at 95 %; 10 % slower at 50 %), although only two to four of the larger activation
+// tiles fit in tensor memory.  A step is in flight for 3-4 thousand cycles (load issue, load latency,
+// conversion, MMA issue, four hand-offs) while its MMAs take a few hundred, so each resource is held
+// only as long as it is needed: an X tile's shared-memory slot (kXSlots = 3) until the converters
+// have read it, a W block's ring slot (kWSlots = 48 blocks) and the activation slot until the step's
+// MMAs are done; the "full" barriers form a ring of kSSlots = 12 steps.  The prologue turns the BCSR
+// rows of the panel into a complete schedule in shared memory -- per step its K-group, the W blocks
+// it needs (kmask of its K-blocks), where each of them sits in the value array (wsrc), its position
+// in the W ring (cum_w), the latest earlier step whose W blocks still occupy that ring space
+// (wait_for) and, per accumulator, the ring slots of its blocks (iss_tab) -- so the roles below run
+// without per-step messages and with almost no bookkeeping of their own; a single warp executes
+// dependent instructions at only one per ~5 cycles, which made run-time bookkeeping the bottleneck
+// of earlier versions.  (With kG = 2 the same source builds the variant with 64-value steps, five X
+// slots, four to six activation slots and issuers that release steps in pairs; K up to 32768 instead
+// of 16384.)
+//   warp 20      X producer: one TMA load per step into the X ring, as soon as the converters have
+//                freed the slot; completes on the step's "full" mbarrier
+//   warps 21-23  W producers: warp j issues the loads of steps j, j + 3, ... (blocks gathered by BCSR
+//                position, one per lane in a single instruction; they complete on the same "full"
+//                mbarrier) once the ring space is free.  Issuing one bulk tensor load costs the issuing
+//                warp 50-140 cycles, hence three warps.
 //   warps 0-3,   converters: shared memory -> registers -> tcgen05.st into the step's slot of the
 //   16-19        activation ring (each warp its own 32-lane quadrant; the two sets alternate steps),
-//                then arrive on the step's "a_full" mbarrier
+//                then arrive on the step's "a_full" mbarrier and on the X slot's "x_free" mbarrier
 //   warps 4-15   MMA issue: warp 4 + l owns accumulator l, and one of its threads issues tcgen05.mma
 //                with A from tensor memory (two K = 16 slabs per W block); MMAs into one accumulator
-//                must come from one thread to stay ordered.  A wait, a commit and an MMA each cost the
-//                issuing thread 80-100 cycles, so every issuer thread counts.  Every issuer commits to
-//                the "empty" mbarrier of every step (also of steps in which it has no block), which
-//                frees the X tile, the W blocks and the activation slot once all twelve have arrived
-//                and makes releases monotonic.
+//                must come from one thread to stay ordered.  Every issuer commits to the "empty"
+//                mbarrier of every step (also of steps in which it has no block), which frees the W
+//                blocks and the activation slot once all have arrived and makes releases monotonic.
+//                What to issue comes from iss_tab; the next step's barrier is probed ahead.
 //   warps 0-3, 16-19 afterwards: epilogue, tcgen05.ld -> + bias -> fp16 / bf16 -> shared memory -> TMA store
 // Every mbarrier wait is bounded; a wait that runs out sets a status word and the CTA winds down.
 //
@@ -56,7 +67,7 @@ using namespace tc;
 
 constexpr int kBlk = 32;            // BCSR block edge (K and N)
 constexpr int kTileM = 128;         // token rows per CTA
-constexpr int kG = 2;               // K-blocks per step (2 or 4; 4 halves the number of steps and measured the same)
+constexpr int kG = 4;               // K-blocks per step (2 or 4, see above)
 constexpr int kSubK = 2 * kBlk;     // K values of one X sub-tile: 128-byte rows, the widest swizzled TMA box
 constexpr int kSubTiles = kG / 2;   // X sub-tiles per step
 constexpr int kSubBytes = kTileM * kSubK * 2;  // 16 KB: 128 rows x 128 B
@@ -67,25 +78,32 @@ constexpr int kACols = kStepK / 2;  // tensor-memory columns of one activation t
 constexpr int kNPMax = 12;          // block columns per CTA: 8, 10 or 12, chosen per launch (template parameter NP)
 constexpr int kMaxKb = kG == 2 ? 1024 : 512;  // K-blocks the schedule can hold (K <= 32768 or 16384): shared-memory budget
 constexpr int kMaxSteps = kMaxKb / kG;
-constexpr int kXSlots = 12 / kG;    // steps whose loads (X tile, W blocks) are in flight: 96 KB of X
-// steps whose activations sit in tensor memory: the tiles that fit beside the NP accumulators, an even
-// number (each slot must always belong to the same converter set), at most kXSlots
+constexpr int kXSlots = kG == 2 ? 5 : 3;  // X tiles in shared memory (80 / 96 KB); a slot is free again once its tile is in tensor memory
+constexpr int kSSlots = 12;         // steps in flight between the first load and the last MMA: size of the "full" barrier ring
+constexpr int kPair = kG == 2 ? 2 : 1;  // steps the issuers release together (pairs 2p, 2p + 1 when steps are small)
+constexpr int kPSlots = kSSlots / kPair;  // ring of the issuers' "empty" barriers
+// steps whose activations sit in tensor memory: the tiles that fit beside the NP accumulators (at most 6)
+constexpr int kASlotsMax = 6;
 constexpr int a_slots(int np) {
-  const int fit = ((512 - np * kBlk) / (kG * kBlk / 2)) & ~1;
-  return fit < kXSlots ? fit : (kXSlots & ~1);
+  const int fit = (512 - np * kBlk) / (kG * kBlk / 2);
+  return fit < kASlotsMax ? fit : kASlotsMax;
 }
-constexpr int kWSlots = kG == 2 ? 40 : 48;    // W blocks in flight
+constexpr int kWSlots = 48;         // W blocks in flight: at least the blocks of a pair of steps, see the W producers
 constexpr int kMmaWarps = 12;       // warps reserved for MMA issue (a multiple of 4); the first NP are used, one per accumulator
 constexpr int kConvSets = 2;        // converter warp sets (four warps each) that alternate steps
-constexpr int kProdWarps = kXSlots < 4 ? kXSlots : 4;  // TMA-issuing warps; at most kXSlots (see the producers' wait)
+constexpr int kProdWarps = 4;       // TMA-issuing warps: one for the X tiles, the others for the W blocks
+constexpr int kWProd = kProdWarps - 1;
 constexpr int kMma0 = 4;            // first MMA-issuing warp
 constexpr int kConv1 = kMma0 + kMmaWarps;    // first warp of the second converter set (a multiple of 4)
 constexpr int kProd0 = kConv1 + 4;  // first producer warp
 constexpr int kThreads = 32 * (kProd0 + kProdWarps);
-static_assert(kProdWarps <= kXSlots, "a producer may run at most one ring turn ahead of the release it waits for");
+static_assert(kWProd <= kSSlots, "a producer may run at most one ring turn ahead of the release it waits for");
+static_assert(kSSlots % 2 == 0 && kSSlots >= kXSlots + kASlotsMax,
+              "the X producer's arrival for step s must find the phase of step s - kSSlots complete, see there");
 static_assert(kConv1 % 4 == 0, "converter warps must map onto their tensor-memory lane quadrant");
 static_assert(kNPMax <= 12 && kNPMax <= kMmaWarps, "a step record packs 12-bit block masks; one issuer warp per accumulator");
-static_assert(kWSlots >= kG * kNPMax && kWSlots < 64, "a step's W blocks must fit the ring; its position packs into 6 bits");
+static_assert(kWSlots >= kPair * kG * kNPMax && kWSlots < 64,
+              "the W blocks of a pair of steps must fit the ring; a ring position packs into 6 bits");
 
 struct DsdTcParams {
   const int32_t* row_ptr;
@@ -98,7 +116,8 @@ struct DsdTcParams {
 };
 
 constexpr uint32_t kTmemCols = 512;
-static_assert(kXSlots * kXBytes >= (kNPMax / 2) * kSubBytes, "the epilogue stages the output tile in the X ring");
+static_assert(kXSlots * kXBytes + kWSlots * kWBytes >= (kNPMax / 2) * kSubBytes,
+              "the epilogue stages the output tile in the X ring and the W ring behind it");
 
 // shared-memory carve-up (byte offsets from a 1 KB aligned base)
 constexpr int kOffX = 0;                                  // X ring   [kXSlots][128 rows x 128 B]
@@ -140,10 +159,11 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   uint64_t* rec = reinterpret_cast<uint64_t*>(smem + kOffRec);
   uint8_t* iss_tab = smem + kOffIss;
   float* s_bias = reinterpret_cast<float*>(smem + kOffBias);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kOffCtl);  // [kXSlots] loads of a step have landed
-  uint64_t* empty_bar = full_bar + kXSlots;                // [kXSlots] MMAs of a step have read their operands
-  uint64_t* afull_bar = empty_bar + kXSlots;               // [kASlots] the step's activations are in tensor memory
-  uint64_t* accum_bar = afull_bar + kASlots;               // [1]       all MMAs of the tile are done
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kOffCtl);  // [kSSlots] loads of a step have landed
+  uint64_t* empty_bar = full_bar + kSSlots;                // [kPSlots] MMAs of a pair of steps have read their operands
+  uint64_t* afull_bar = empty_bar + kPSlots;               // [kASlots] the step's activations are in tensor memory
+  uint64_t* xfree_bar = afull_bar + kASlots;               // [kXSlots] the X tile has been read out of its slot
+  uint64_t* accum_bar = xfree_bar + kXSlots;               // [1]       all MMAs of the tile are done
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum_bar + 1);
   int* s_range = reinterpret_cast<int*>(tmem_holder + 1);  // [2] BCSR entries of the panel
   int* s_nsteps = s_range + 2;
@@ -160,11 +180,10 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
   // ------------------------------ prologue: barriers, tensor memory, schedule ------------------------------
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kXSlots; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], kIssuers);
-    }
+    for (int s = 0; s < kSSlots; ++s) mbar_init(&full_bar[s], 2);  // the X producer and the step's W producer
+    for (int s = 0; s < kPSlots; ++s) mbar_init(&empty_bar[s], kIssuers);
     for (int s = 0; s < kASlots; ++s) mbar_init(&afull_bar[s], 4);
+    for (int s = 0; s < kXSlots; ++s) mbar_init(&xfree_bar[s], 4);
     mbar_init(accum_bar, kIssuers);
     fence_mbar_init();
     s_range[0] = p.row_ptr[nb0];
@@ -237,8 +256,8 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   }
   __syncthreads();
   const int n_steps = *s_nsteps;
-  // step s may be issued once the step that last used its X slot (s - kXSlots) and step wait_for[s], the
-  // latest one whose W blocks still occupy the ring positions s needs, have been released
+  // the W blocks of step s may be fetched once step wait_for[s], the latest one whose W blocks still
+  // occupy the ring positions s needs, has been released
   for (int s = threadIdx.x; s < n_steps; s += kThreads) {
     const int target = static_cast<int>(cum_w[s + 1]) - kWSlots;
     int f = -1;
@@ -279,14 +298,37 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const uint32_t a_tmem = tmem_base + kAccCols;  // activation ring
 
   bool failed = false;  // a bounded wait of this thread gave up
-  if (warp >= kProd0) {
-    // ------------------------------ producers ------------------------------
-    // W blocks: one instruction per pair of K-blocks; lanes 0 .. NP-1 fetch the blocks of the pair's
-    // first K-block, lanes 16 .. 16+NP-1 those of the second
+  if (warp == kProd0) {
+    // ------------------------------ X producer ------------------------------
+    // One warp, all steps in order: the slot is free once the converters have read the tile that was
+    // in it (step s - kXSlots).  The converter of that step had waited for the release of step
+    // s - kXSlots - kASlots, so the issuers -- and before them the converters -- are through every step
+    // up to there, step s - kSSlots included: the previous phase of this step's "full" barrier is
+    // complete when the arrival for step s is made.
+    bool ok = true;
+    for (int s = 0; s < n_steps; ++s) {
+      const int xslot = s % kXSlots, sslot = s % kSSlots;
+      if (s >= kXSlots && !mbar_wait_warp(&xfree_bar[xslot], ((s - kXSlots) / kXSlots) & 1)) { ok = false; break; }
+      if (lane == 0) {
+        const int kp = step_kp[s];
+        mbar_arrive_expect_tx(&full_bar[sslot], kXBytes);
+#pragma unroll
+        for (int t = 0; t < kSubTiles; ++t)
+          tma_load_2d(x_ring + xslot * kXBytes + t * kSubBytes, &tm_x, kp * kStepK + t * kSubK, batch * p.M + m0,
+                      &full_bar[sslot]);
+      }
+      __syncwarp();
+    }
+    failed |= !ok;
+    if (!ok && lane == 0) atomicExch(&p.status[0], 1);
+  } else if (warp > kProd0) {
+    // ------------------------------ W producers ------------------------------
+    // One instruction per pair of K-blocks; lanes 0 .. NP-1 fetch the blocks of the pair's first
+    // K-block, lanes 16 .. 16+NP-1 those of the second
     const long long wrow0 = ((long long)batch * p.val_stride_blocks + e0) * kBlk;  // row in the [blocks * 32, 32] view
     const int half = lane >> 4, l = lane & 15;
     bool ok = true;
-    for (int s = warp - kProd0; s < n_steps; s += kProdWarps) {
+    for (int s = warp - kProd0 - 1; s < n_steps; s += kWProd) {
       const int kp = step_kp[s];
       const uint64_t r = rec[s];
       const int c0 = static_cast<int>(r >> 48) & 0x3f, wf = wait_for[s];
@@ -300,19 +342,16 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       }
       // An mbarrier wait names a phase by its parity only, so a waiter must know that the barrier is
       // at most one phase away from the one it names.  Releases are monotonic and this warp's previous
-      // step (s - kProdWarps) confirmed the release of step s - kProdWarps - kXSlots, the predecessor of
-      // step s - kXSlots on this slot's barrier: waiting for s - kXSlots is safe.  After it, everything
-      // up to s - kXSlots is known to be released, which covers the predecessor of any later step wf.
-      if (s >= kXSlots && !mbar_wait_warp(&empty_bar[s % kXSlots], ((s - kXSlots) / kXSlots) & 1)) { ok = false; break; }
-      if (wf >= 0 && wf > s - kXSlots && !mbar_wait_warp(&empty_bar[wf % kXSlots], (wf / kXSlots) & 1)) { ok = false; break; }
-      const int slot = s % kXSlots;
-      if (lane == 0) {
-        mbar_arrive_expect_tx(&full_bar[slot], kXBytes + n_blocks * kWBytes);
-#pragma unroll
-        for (int t = 0; t < kSubTiles; ++t)
-          tma_load_2d(x_ring + slot * kXBytes + t * kSubBytes, &tm_x, kp * kStepK + t * kSubK, batch * p.M + m0,
-                      &full_bar[slot]);
-      }
+      // step (s - kWProd) confirmed the release of step s - kWProd - kSSlots, at or after the predecessor
+      // of step s - kSSlots on that barrier: waiting for s - kSSlots is safe.  After it, everything up to
+      // s - kSSlots is known to be released, which covers the predecessor of any later step wf, and the
+      // previous phase of this step's "full" barrier is complete.
+      // Steps are released in pairs: step t with pair t / 2, on barrier (t / 2) % kPSlots.  wait_for[s]
+      // always lies in an earlier pair than s, because the blocks of one pair fit the ring.
+      const int sslot = s % kSSlots, pr = s / kPair;
+      if (s >= kSSlots && !mbar_wait_warp(&empty_bar[pr % kPSlots], (pr / kPSlots - 1) & 1)) { ok = false; break; }
+      if (wf >= 0 && wf > s - kSSlots && !mbar_wait_warp(&empty_bar[(wf / kPair) % kPSlots], ((wf / kPair) / kPSlots) & 1)) { ok = false; break; }
+      if (lane == 0) mbar_arrive_expect_tx(&full_bar[sslot], n_blocks * kWBytes);
       __syncwarp();  // the expected byte count is registered before any lane's load can complete
       int before = c0;  // ring position of the pair's first block
 #pragma unroll
@@ -320,7 +359,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         if ((pack[t] >> lane) & 1u) {
           int ws = before + __popc(pack[t] & ((1u << lane) - 1u));  // rank among the step's blocks
           if (ws >= kWSlots) ws -= kWSlots;
-          tma_load_2d(w_ring + ws * kWBytes, &tm_w, 0, (int)(wrow0 + (long long)src[t] * kBlk), &full_bar[slot]);
+          tma_load_2d(w_ring + ws * kWBytes, &tm_w, 0, (int)(wrow0 + (long long)src[t] * kBlk), &full_bar[sslot]);
         }
         before += __popc(pack[t]);
       }
@@ -340,44 +379,57 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     using Word = typename std::conditional<kG == 2, uint16_t, uint32_t>::type;  // kG bytes of the table
     constexpr uint32_t kNone = kG == 2 ? 0xffffu : 0xffffffffu;
     const Word* tab = reinterpret_cast<const Word*>(iss_tab) + l;
-    uint32_t slot = 0, aslot = 0, aphase = 0, accumulate = 0;
+    uint32_t pslot = 0, aslot = 0, aphase = 0, accumulate = 0;
     bool ok = true;
-    uint32_t v_next = n_steps > 0 ? tab[0] : kNone;
-    bool ready = false;  // the next step's activations were seen in place by the probe of the step before
-    for (int s = 0; s < n_steps; ++s) {
-      const uint32_t v = v_next;
-      if (s + 1 < n_steps) v_next = tab[(s + 1) * NP];  // fetched ahead of the wait
-      // Every issuer waits for the activations of every step and commits to its "empty" barrier, also
-      // in a step in which it has no block.  The wait keeps it within one ring turn of the converters,
-      // so a phase parity is never mistaken for an older one; the commit makes the release of steps
-      // monotonic (a released step implies that every issuer's MMAs of all earlier steps are done),
-      // which is what the producers' wait_for table assumes.  The step's "full" phase completed before
-      // its converters ran, so the W blocks are in place too.  What to issue comes from the table the
-      // prologue built: decoding the step's masks here, on one warp, took longer than the MMAs.
-      if (!ready && !mbar_wait(&afull_bar[aslot], aphase)) { ok = false; break; }
-      if (v != kNone) {
-        tc_fence_after_sync();
-        if (leader) {
+    // the MMAs of one step of this accumulator: v holds, per K-block of the step, the W ring slot or 0xff
+    auto issue = [&](uint32_t v, uint32_t as) {
 #pragma unroll
-          for (int j = 0; j < kG; ++j) {
-            const uint32_t b = (v >> (8 * j)) & 0xffu;
-            if (b != 0xffu) {
-              const uint32_t a_addr = a_tmem + aslot * kACols + j * (kBlk / 2);
-              const uint32_t b_lo = w_base16 + b * (kWBytes >> 4);
-              umma_ts(d_tmem, a_addr, desc_hi | b_lo, idesc, accumulate);
-              umma_ts(d_tmem, a_addr + kBlk / 4, desc_hi | (b_lo + 2), idesc, 1u);
-              accumulate = 1u;
-            }
-          }
+      for (int j = 0; j < kG; ++j) {
+        const uint32_t b = (v >> (8 * j)) & 0xffu;
+        if (b != 0xffu) {
+          const uint32_t a_addr = a_tmem + as * kACols + j * (kBlk / 2);
+          const uint32_t b_lo = w_base16 + b * (kWBytes >> 4);
+          umma_ts(d_tmem, a_addr, desc_hi | b_lo, idesc, accumulate);
+          umma_ts(d_tmem, a_addr + kBlk / 4, desc_hi | (b_lo + 2), idesc, 1u);
+          accumulate = 1u;
         }
       }
-      // The issuers usually run a few steps behind the converters: probe the next step's barrier now, so
-      // that the round trip of the probe overlaps the commit instead of opening the next iteration.
-      const uint32_t slot_done = slot;
-      if (++slot == kXSlots) slot = 0;
+    };
+    // Steps are taken two at a time.  Every issuer waits for the activations of every step and commits
+    // to the "empty" barrier of every pair, also when it has no block in it.  The waits keep it within
+    // one ring turn of the converters, so a phase parity is never mistaken for an older one; the commit
+    // makes the release of steps monotonic (a released pair implies that every issuer's MMAs of all
+    // earlier steps are done), which is what the producers' wait_for table assumes.  A step's "full"
+    // phase completed before its converters ran, so the W blocks are in place too.  What to issue
+    // comes from the table the prologue built: decoding the step's masks here, on one warp, took
+    // longer than the MMAs.  The wait, the commit and the loop cost a warp 200-300 cycles, several
+    // times the MMAs of a step: hence pairs, and the probes of the next pair's barriers issued ahead
+    // (the issuers usually run a few steps behind the converters, so the probes mostly succeed).
+    bool ready0 = false, ready1 = false;
+    for (int s = 0; s < n_steps; s += kPair) {
+      const bool two = kPair == 2 && s + 1 < n_steps;
+      const uint32_t v0 = tab[s * NP], v1 = two ? static_cast<uint32_t>(tab[(s + 1) * NP]) : kNone;
+      const uint32_t as0 = aslot, ph0 = aphase;
       if (++aslot == kASlots) { aslot = 0; aphase ^= 1u; }
-      ready = s + 1 < n_steps && mbar_test_wait(&afull_bar[aslot], aphase);
-      if (leader) umma_commit(&empty_bar[slot_done]);  // frees the step's X tile, W blocks and activation slot
+      const uint32_t as1 = aslot, ph1 = aphase;
+      if (kPair == 2 && ++aslot == kASlots) { aslot = 0; aphase ^= 1u; }
+      if (!ready0 && !mbar_wait(&afull_bar[as0], ph0)) { ok = false; break; }
+      if (v0 != kNone) {
+        tc_fence_after_sync();
+        if (leader) issue(v0, as0);
+      }
+      if (two) {
+        if (!ready1 && !mbar_wait(&afull_bar[as1], ph1)) { ok = false; break; }
+        if (v1 != kNone) {
+          tc_fence_after_sync();
+          if (leader) issue(v1, as1);
+        }
+      }
+      const uint32_t as3 = aslot + 1 == kASlots ? 0u : aslot + 1, ph3 = aslot + 1 == kASlots ? aphase ^ 1u : aphase;
+      ready0 = s + kPair < n_steps && mbar_test_wait(&afull_bar[aslot], aphase);
+      ready1 = kPair == 2 && s + 3 < n_steps && mbar_test_wait(&afull_bar[as3], ph3);
+      if (leader) umma_commit(&empty_bar[pslot]);  // frees the pair's W blocks and activation slots
+      if (++pslot == kPSlots) pslot = 0;
     }
     failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[1], 1);
@@ -394,8 +446,8 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       const int slot = s % kXSlots, aslot = s % kASlots;
       // the activation slot is free once the MMAs of step s - kASlots are done (this warp confirmed the
       // release of step s - kConvSets - kASlots on its previous turn, so the parity cannot alias)
-      if (s >= kASlots && !mbar_wait_warp(&empty_bar[(s - kASlots) % kXSlots], ((s - kASlots) / kXSlots) & 1)) { ok = false; break; }
-      if (!mbar_wait_warp(&full_bar[slot], (s / kXSlots) & 1)) { ok = false; break; }
+      if (s >= kASlots && !mbar_wait_warp(&empty_bar[((s - kASlots) / kPair) % kPSlots], (((s - kASlots) / kPair) / kPSlots) & 1)) { ok = false; break; }
+      if (!mbar_wait_warp(&full_bar[s % kSSlots], (s / kSSlots) & 1)) { ok = false; break; }
 #pragma unroll
       for (int t = 0; t < kSubTiles; ++t) {
         const uint8_t* xrow = x_ring + slot * kXBytes + t * kSubBytes + row * (kSubK * 2);
@@ -410,7 +462,10 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&afull_bar[aslot]);
+      if (lane == 0) {
+        mbar_arrive(&afull_bar[aslot]);
+        mbar_arrive(&xfree_bar[slot]);  // the tile is in registers / tensor memory: the X slot may be refilled
+      }
     }
     failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[3], 1);

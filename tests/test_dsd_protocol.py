@@ -1,6 +1,8 @@
 """Discrete-event simulation of the mbarrier protocol of the tcgen05 dsd kernel
-(``sparta_b200/csrc/bsmm_dsd_tc.cu``): four producer warps, two converter sets, twelve issuers, rings
-of 6 load slots / 4 or 6 activation slots / 40 W blocks, waits that name a phase by its parity only.
+(``sparta_b200/csrc/bsmm_dsd_tc.cu``): one X producer warp, three W producer warps, two converter sets,
+one issuer warp per block column; a ring of 12 steps for the "full" barriers, X slots in shared memory
+that the converters free, activation slots in tensor memory and a ring of 48 W blocks that the issuers
+free (per step or per pair of steps); waits that name a phase by its parity only.
 
 The simulation runs the roles' wait / arrive sequences under random timing with the mbarrier rules
 (a wait for parity P succeeds when the barrier's current phase has the other parity; an arrival beyond
@@ -14,7 +16,7 @@ import random
 import numpy as np
 import pytest
 
-NP, KX, KW, NPROD = 12, 6, 40, 4
+KS, KW, NWPROD = 12, 48, 3
 
 
 class Barrier:
@@ -45,15 +47,20 @@ def wait_for_table(need):
     return cum, table
 
 
-def simulate(need, seed, KA=4, NISS=12):
-    """KA activation slots in tensor memory, NISS issuer warps (4 / 12 for panels of 12 block columns,
-    6 / 10 for panels of 10, 6 / 8 for panels of 8)."""
+def simulate(need, seed, KA=3, NISS=10, KX=3, PAIR=1):
+    """KA activation slots in tensor memory, NISS issuer warps (one per block column of the panel), KX
+    X slots in shared memory, PAIR steps released together by the issuers.  The kernel as built
+    (four K-blocks per step): KX 3, PAIR 1 and KA / NISS of 2 / 12, 3 / 10 or 4 / 8; its variant with two
+    K-blocks per step: KX 5, PAIR 2 and 4 / 12, 6 / 10 or 6 / 8."""
+    KP = KS // PAIR
     rnd = random.Random(seed)
     n = len(need)
     cum, wait_for = wait_for_table(need)
-    full = [Barrier(1, f'full{i}') for i in range(KX)]
-    empty = [Barrier(NISS, f'empty{i}') for i in range(KX)]
+    full = [Barrier(2, f'full{i}') for i in range(KS)]      # X producer + W producer
+    empty = [Barrier(NISS, f'empty{i}') for i in range(KP)]
+    pair_wait = lambda t: ('wait', empty[(t // PAIR) % KP], ((t // PAIR) // KP) & 1)  # release of step t
     afull = [Barrier(4, f'afull{i}') for i in range(KA)]
+    xfree = [Barrier(4, f'xfree{i}') for i in range(KX)]
     accum = Barrier(NISS, 'accum')
     x_owner = [None] * KX   # step whose X tile sits in the shared-memory slot
     a_owner = [None] * KA   # step whose activations sit in the tensor-memory slot
@@ -61,51 +68,61 @@ def simulate(need, seed, KA=4, NISS=12):
     mma_left = [NISS] * n
     jitter = rnd.uniform
 
-    def producer(j):
-        for s in range(j, n, NPROD):
-            slot = s % KX
-            if s >= KX:  # own slot's previous use: the barrier's next use is s itself
-                yield ('wait', empty[slot], ((s - KX) // KX) & 1)
+    def x_producer():
+        for s in range(n):
+            xslot = s % KX
+            if s >= KX:  # the converters have read the slot's previous tile (one warp, in order: no aliasing)
+                yield ('wait', xfree[xslot], ((s - KX) // KX) & 1)
+            yield ('delay', jitter(50, 300))
+            assert x_owner[xslot] is None, f'X slot {xslot} overwritten: holds {x_owner[xslot]}, new {s}'
+            x_owner[xslot] = s
+            yield ('delay', jitter(200, 1200))  # the load lands
+            yield ('arrive', full[s % KS], 1)
+
+    def w_producer(j):
+        for s in range(j, n, NWPROD):
+            if s >= KS:  # own barrier slot's previous use: the barrier's next use is s itself
+                yield pair_wait(s - KS)
             wf = wait_for[s]
-            if wf >= 0 and wf > s - KX:  # previous use of that barrier is known released, next use > s
-                yield ('wait', empty[wf % KX], (wf // KX) & 1)
+            if wf >= 0 and wf > s - KS:  # previous use of that barrier is known released, next use > s
+                yield pair_wait(wf)
             yield ('delay', jitter(100, 600))
-            assert x_owner[slot] is None, f'X slot {slot} overwritten: holds {x_owner[slot]}, new {s}'
-            x_owner[slot] = s
             for q in range(cum[s], cum[s + 1]):
                 assert q % KW not in w_owner, f'W slot {q % KW} of step {w_owner.get(q % KW)} overwritten by {s}'
                 w_owner[q % KW] = s
             yield ('delay', jitter(200, 1200))  # the loads land
-            yield ('arrive', full[slot], 1)
+            yield ('arrive', full[s % KS], 1)
 
     def converter(c):
         for s in range(c, n, 2):
-            slot, aslot = s % KX, s % KA
+            xslot, aslot = s % KX, s % KA
             if s >= KA:
-                yield ('wait', empty[(s - KA) % KX], ((s - KA) // KX) & 1)
-            yield ('wait', full[slot], (s // KX) & 1)
-            assert x_owner[slot] == s, f'converter of step {s} reads X slot holding {x_owner[slot]}'
+                yield pair_wait(s - KA)
+            yield ('wait', full[s % KS], (s // KS) & 1)
+            assert x_owner[xslot] == s, f'converter of step {s} reads X slot holding {x_owner[xslot]}'
             yield ('delay', jitter(100, 400))
             assert a_owner[aslot] is None, f'A slot {aslot} of step {a_owner[aslot]} overwritten by {s}'
             a_owner[aslot] = s
+            x_owner[xslot] = None
             yield ('arrive', afull[aslot], 4)  # the set's four warps
+            yield ('arrive', xfree[xslot], 4)
 
     def issuer(i):
         for s in range(n):
-            slot, aslot = s % KX, s % KA
+            slot, aslot = s % KS, s % KA
             yield ('wait', afull[aslot], (s // KA) & 1)
             assert a_owner[aslot] == s, f'issuer {i} at step {s} reads A slot holding {a_owner[aslot]}'
             yield ('delay', jitter(50, 700) if rnd.random() < 0.5 else jitter(20, 100))
             mma_left[s] -= 1
             if mma_left[s] == 0:  # the step's operands are dead
                 a_owner[aslot] = None
-                x_owner[slot] = None
                 for q in range(cum[s], cum[s + 1]):
                     del w_owner[q % KW]
-            yield ('arrive', empty[slot], 1)
+            if s % PAIR == PAIR - 1 or s == n - 1:
+                yield ('arrive', empty[(s // PAIR) % KP], 1)
         yield ('arrive', accum, 1)
 
-    roles = [producer(j) for j in range(NPROD)] + [converter(0), converter(1)] + [issuer(i) for i in range(NISS)]
+    roles = [x_producer()] + [w_producer(j) for j in range(NWPROD)] + [converter(0), converter(1)] + [issuer(i) for i in range(NISS)]
     now = 0.0
     ready = [(0.0, k) for k in range(len(roles))]
     heapq.heapify(ready)
@@ -137,17 +154,22 @@ def simulate(need, seed, KA=4, NISS=12):
     assert not w_owner and all(o is None for o in x_owner) and all(o is None for o in a_owner)
 
 
-@pytest.mark.parametrize('ka,niss', [(4, 12), (6, 10), (6, 8)])
+# (activation slots, issuers, X slots, steps released together, K-blocks per step)
+CONFIGS = [(2, 12, 3, 1, 4), (3, 10, 3, 1, 4), (4, 8, 3, 1, 4),     # the kernel as built
+           (4, 12, 5, 2, 2), (6, 10, 5, 2, 2), (6, 8, 5, 2, 2)]     # its variant with two K-blocks per step
+
+
+@pytest.mark.parametrize('ka,niss,kx,pair,kg', CONFIGS)
 @pytest.mark.parametrize('density', [0.02, 0.1, 0.25, 0.5, 1.0])
-def test_protocol_under_random_timing(density, ka, niss):
+def test_protocol_under_random_timing(density, ka, niss, kx, pair, kg):
     rs = np.random.RandomState(int(density * 1000) + ka)
-    for trial in range(8):
-        need = np.maximum(1, rs.binomial(2 * niss, density, size=rs.randint(1, 100)))
-        simulate(need, seed=trial, KA=ka, NISS=niss)
+    for trial in range(6):
+        need = np.maximum(1, rs.binomial(kg * niss, density, size=rs.randint(1, 100)))
+        simulate(need, seed=trial, KA=ka, NISS=niss, KX=kx, PAIR=pair)
 
 
 def test_wait_for_table_small_case():
-    # ring of 40: step 3 needs positions 36..47, i.e. the space of steps 0 (12 blocks); step 4 wraps further
-    cum, table = wait_for_table(np.array([12, 12, 12, 12, 12]))
-    assert list(cum) == [0, 12, 24, 36, 48, 60]
-    assert table == [-1, -1, -1, 0, 1]
+    # ring of 48: step 2 needs positions 40..59, i.e. the space of step 0 (20 blocks); step 3 wraps further
+    cum, table = wait_for_table(np.array([20, 20, 20, 20, 20]))
+    assert list(cum) == [0, 20, 40, 60, 80, 100]
+    assert table == [-1, -1, 0, 1, 2]
