@@ -51,7 +51,8 @@
 //                mbarrier of every step (also of steps in which it has no block), which frees the W
 //                blocks and the activation slot once all have arrived and makes releases monotonic.
 //                What to issue comes from iss_tab; the next step's barrier is probed ahead.
-//   warps 0-3, 16-19 afterwards: epilogue, tcgen05.ld -> + bias -> fp16 / bf16 -> shared memory -> TMA store
+//   warps 0-3, 16-19 afterwards: epilogue, tcgen05.ld -> + bias -> fp16 / bf16 -> shared memory -> one TMA
+//                store per tile of 64 output columns, issued as soon as the tile's four warps are done
 // Every mbarrier wait is bounded; a wait that runs out sets a status word and the CTA winds down.
 //
 // Replaces sparta_sparse_matmul_dsd.cuh.j2 / openai_sparse_matmul_dsd.cuh.j2 for this layout.
@@ -476,53 +477,60 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     // would touch 32 different lines with every instruction and took four times longer.)  The two
     // warps of a lane quadrant take alternate pairs of accumulators.
     const uint32_t written = *s_written;
-    if (!mbar_wait_warp(accum_bar, 0)) {
+    const bool acc_ok = mbar_wait_warp(accum_bar, 0);
+    if (!acc_ok) {
       failed = true;
       if (lane == 0) atomicExch(&p.status[2], 1);
     } else {
       tc_fence_after_sync();
-      const int n_acc = nb_end - nb0;
-      for (int l = 0; l < n_acc; ++l) {
-        if (((l >> 1) & 1) != conv_set) continue;
-        uint32_t r[32];
-        if ((written >> l) & 1u) {
-          tmem_ld_x32(tmem_base + lane_addr + l * kBlk, r);
-          tmem_ld_wait();
-        } else {
+    }
+    // A tile (two accumulators, 64 output columns) belongs to one converter set; its four warps fill
+    // it, meet at the set's named barrier, and one thread issues the tile's TMA store while the set
+    // goes on to its next tile.
+    const int n_acc = nb_end - nb0, n_tiles = (n_acc + 1) / 2;
+    for (int t = conv_set; t < n_tiles; t += kConvSets) {
+      if (acc_ok) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = 0;
-        }
-        uint32_t packed[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float2 bv = *reinterpret_cast<const float2*>(&s_bias[l * kBlk + 2 * j]);
-          const float v0 = __uint_as_float(r[2 * j]) + bv.x, v1 = __uint_as_float(r[2 * j + 1]) + bv.y;
-          if constexpr (FMT == 0) {
-            __half2 h = __floats2half2_rn(v0, v1);
-            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+        for (int h = 0; h < 2; ++h) {
+          const int l = 2 * t + h;
+          if (l >= n_acc) break;
+          uint32_t r[32];
+          if ((written >> l) & 1u) {
+            tmem_ld_x32(tmem_base + lane_addr + l * kBlk, r);
+            tmem_ld_wait();
           } else {
-            __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0;
+          }
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float2 bv = *reinterpret_cast<const float2*>(&s_bias[l * kBlk + 2 * j]);
+            const float v0 = __uint_as_float(r[2 * j]) + bv.x, v1 = __uint_as_float(r[2 * j + 1]) + bv.y;
+            if constexpr (FMT == 0) {
+              __half2 hh = __floats2half2_rn(v0, v1);
+              packed[j] = *reinterpret_cast<uint32_t*>(&hh);
+            } else {
+              __nv_bfloat162 hh = __floats2bfloat162_rn(v0, v1);
+              packed[j] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+          }
+          // tile t, row `row`, 16-byte chunks h * 4 .. + 3, each at chunk position c ^ (row & 7)
+          uint8_t* trow = x_ring + t * kSubBytes + row * 128;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t c = static_cast<uint32_t>(h * 4 + j) ^ sw;
+            *reinterpret_cast<uint4*>(trow + (c << 4)) =
+                make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
           }
         }
-        // tile l / 2, row `row`, 16-byte chunks (l % 2) * 4 .. + 3, each at chunk position c ^ (row & 7)
-        uint8_t* trow = x_ring + (l >> 1) * kSubBytes + row * 128;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t c = static_cast<uint32_t>((l & 1) * 4 + j) ^ sw;
-          *reinterpret_cast<uint4*>(trow + (c << 4)) =
-              make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-        }
+        fence_proxy_async_smem();  // the tile was written through the generic proxy, TMA reads through the async one
       }
-      fence_proxy_async_smem();  // the tiles were written through the generic proxy, TMA reads through the async one
-    }
-    named_barrier_sync(1, 8 * 32);  // the eight epilogue warps
-    if (warp == 0 && lane == 0 && !failed) {
-      const int n_tiles = (nb_end - nb0 + 1) / 2;
-      for (int t = 0; t < n_tiles; ++t)
+      if (conv_set == 0) named_barrier_sync(2, 4 * 32); else named_barrier_sync(3, 4 * 32);  // the four warps of this set
+      if (quad == 0 && lane == 0 && acc_ok)
         tma_store_2d(&tm_c, x_ring + t * kSubBytes, (nb0 + 2 * t) * kBlk, batch * p.M + m0);
-      tma_store_commit_and_wait();
     }
+    if (quad == 0 && lane == 0) tma_store_commit_and_wait();  // shared memory must outlive the stores' reads
   }
   tc_fence_before_sync();
   sync_and_drain(failed);
