@@ -180,6 +180,10 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const int n_pairs = (p.Kb + kG - 1) / kG;  // K-groups (steps before the empty ones are dropped)
 
   // ------------------------------ prologue: barriers, tensor memory, schedule ------------------------------
+  // the rows of a panel are consecutive in the BCSR array; every thread reads the panel's range and its
+  // first entry now, so that the two dependent trips to memory overlap the set-up below
+  const int e0 = __ldg(p.row_ptr + nb0), e1 = __ldg(p.row_ptr + nb_end);
+  const int v_first = e0 + static_cast<int>(threadIdx.x) < e1 ? __ldg(p.idx + e0 + threadIdx.x) : 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSSlots; ++s) mbar_init(&full_bar[s], 2);  // the X producer and the step's W producer
     for (int s = 0; s < kPSlots; ++s) mbar_init(&empty_bar[s], kIssuers);
@@ -187,8 +191,6 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     for (int s = 0; s < kXSlots; ++s) mbar_init(&xfree_bar[s], 4);
     mbar_init(accum_bar, kIssuers);
     fence_mbar_init();
-    s_range[0] = p.row_ptr[nb0];
-    s_range[1] = p.row_ptr[nb_end];
   }
   if (warp == kProd0 && lane == 0) {
     prefetch_tensormap(&tm_x);
@@ -205,10 +207,9 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
   }
   __syncthreads();
-  // the rows of a panel are consecutive in the BCSR array: entry = (row-block << 16) | K-block
-  const int e0 = s_range[0];
-  for (int e = e0 + threadIdx.x; e < s_range[1]; e += kThreads) {
-    const int v = __ldg(p.idx + e);
+  // entry = (row-block << 16) | K-block
+  for (int e = e0 + threadIdx.x; e < e1; e += kThreads) {
+    const int v = e == e0 + static_cast<int>(threadIdx.x) ? v_first : __ldg(p.idx + e);
     const int k = v & 0xffff, l = (v >> 16) - nb0;
     if (k < p.Kb && l >= 0 && l < NP) {  // index arrays come from the caller: never index shared memory with them unchecked
       atomicOr(&kmask[k], 1u << l);
@@ -276,20 +277,24 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll
     for (int j = 0; j < kG; ++j) rr |= static_cast<uint64_t>(kmask[kG * kp + j]) << (NP * j);
     rec[s] = rr;
-    // the issuers' view of the step: for every accumulator and K-block of the step, the W ring slot that
-    // holds its block (blocks take consecutive slots in K-block, then accumulator order)
+  }
+  // the issuers' view of a step: for every accumulator and K-block of the step, the W ring slot that
+  // holds its block (blocks take consecutive slots in K-block, then accumulator order), 0xff for none
+  for (int i = threadIdx.x; i < n_steps * NP; i += kThreads) {
+    const int s = i / NP, l = i - s * NP;
+    const int kp = step_kp[s];
     int pos = static_cast<int>(cum_w[s] % kWSlots);
 #pragma unroll
     for (int j = 0; j < kG; ++j) {
       const uint32_t mk = kmask[kG * kp + j];
-      for (int l = 0; l < NP; ++l) {
-        uint8_t b = 0xff;
-        if ((mk >> l) & 1u) {
-          b = static_cast<uint8_t>(pos);
-          if (++pos == kWSlots) pos = 0;
-        }
-        iss_tab[(s * NP + l) * kG + j] = b;
+      uint8_t b = 0xff;
+      if ((mk >> l) & 1u) {
+        int q = pos + __popc(mk & ((1u << l) - 1u));  // below 2 kWSlots: a step holds at most kWSlots blocks
+        if (q >= kWSlots) q -= kWSlots;
+        b = static_cast<uint8_t>(q);
       }
+      iss_tab[i * kG + j] = b;
+      pos += __popc(mk);
     }
   }
   tc_fence_before_sync();
