@@ -31,6 +31,15 @@ constexpr int kThreads = 224;
 constexpr int kMaxKb = 1024;   // K blocks per row (Ns <= 65536)
 constexpr float kRescaleThreshold = 8.f;
 
+// 2^x by the special-function unit alone.  exp2f() wraps the same instruction in a range fix for
+// results below the normal range (a compare, two multiplies); probabilities that small round to zero
+// in fp16 / bf16 anyway, and the softmax warps are bound by the number of instructions they issue.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct AttnParams {
   const int32_t* row_ptr;
   const int32_t* idx;
@@ -311,8 +320,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             float sum = 0.f;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              float p0 = exp2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_run));
-              float p1 = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_run));
+              float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_run));
+              float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_run));
               if (p.mask) {
                 if (!((mw[(2 * i) >> 2] >> (8 * ((2 * i) & 3))) & 0xffu)) p0 = 0.f;
                 if (!((mw[(2 * i + 1) >> 2] >> (8 * ((2 * i + 1) & 3))) & 0xffu)) p1 = 0.f;
