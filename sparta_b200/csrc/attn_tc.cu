@@ -308,7 +308,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             uint32_t r[32];
             tmem_ld_x32(s_addr + b * kBlk + h * 32, r);
             tmem_ld_wait();
-            const bool dead = !(m_run > -INFINITY);  // every score of this row masked so far
+            // every score of this row masked so far: subtracting +inf makes every probability zero
+            const float neg_m = m_run > -INFINITY ? -m_run : -INFINITY;
             uint32_t mw[8];
             if (p.mask) {
               const uint8_t* mrow = p.mask + grow * p.Ns + (long long)kb[b] * kBlk + h * 32;
@@ -320,23 +321,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             float sum = 0.f;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_run));
-              float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_run));
+              float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, neg_m));
+              float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, neg_m));
               if (p.mask) {
                 if (!((mw[(2 * i) >> 2] >> (8 * ((2 * i) & 3))) & 0xffu)) p0 = 0.f;
                 if (!((mw[(2 * i + 1) >> 2] >> (8 * ((2 * i + 1) & 3))) & 0xffu)) p1 = 0.f;
               }
-              if (dead) p0 = p1 = 0.f;
+              // the row sum takes the fp32 probabilities: their rounding to 16 bits for P V is unbiased, and
+              // converting them back cost two instructions per pair in warps bound by instruction issue
+              sum += p0 + p1;
               if constexpr (FMT == 0) {
                 const __half2 hv = __floats2half2_rn(p0, p1);
                 packed[i] = *reinterpret_cast<const uint32_t*>(&hv);
-                const float2 back = __half22float2(hv);
-                sum += back.x + back.y;  // the sum uses the rounded values that enter P V
               } else {
                 const __nv_bfloat162 hv = __floats2bfloat162_rn(p0, p1);
                 packed[i] = *reinterpret_cast<const uint32_t*>(&hv);
-                const float2 back = __bfloat1622float2(hv);
-                sum += back.x + back.y;
               }
             }
             l_run += sum;
