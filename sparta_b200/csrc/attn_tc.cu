@@ -11,9 +11,9 @@
 //   S[128, 128] = Q[128, D] . [K_a; K_b]^T           (tcgen05.mma M128 N128, D/16 of them)
 //   P = exp2(S * scale * log2e - m)  in registers, masked per row half and per element, -> smem
 //   O[128, D] += P[128, 128] . [V_a; V_b]             (tcgen05.mma M128 N=D, B operand MN-major)
-// Warps: 0-3 softmax (one row per thread, online max / sum with a lazy rescale of O: the running max
-// is only raised when it grows by more than 8 in log2 units), 4 TMA producer, 5 issues the Q.K^T
-// MMAs, 6 issues the P.V MMAs.  All mbarrier waits are bounded (status words of sparta_last_status).
+// Warps: 0-7 softmax (two threads per row, one for each K block of the pair; online max / sum with a
+// lazy rescale of O: the running max is only raised when it grows by more than 8 in log2 units), 8 TMA
+// producer, 9 issues the Q.K^T MMAs, 10 issues the P.V MMAs.  All mbarrier waits are bounded (status words of sparta_last_status).
 #include <type_traits>
 
 #include "bsmm.cuh"
@@ -27,7 +27,9 @@ using namespace tc;
 constexpr int kBlk = 64;       // mask block edge
 constexpr int kTileM = 128;    // Q rows per CTA
 constexpr int kPair = 128;     // keys per step (two blocks)
-constexpr int kThreads = 224;
+constexpr int kSoftmaxWarps = 8;  // two per tensor-memory lane quadrant: one for each K block of a pair
+constexpr int kWarpLoad = kSoftmaxWarps, kWarpQK = kSoftmaxWarps + 1, kWarpPV = kSoftmaxWarps + 2;
+constexpr int kThreads = 32 * (kSoftmaxWarps + 3);
 constexpr int kMaxKb = 1024;   // K blocks per row (Ns <= 65536)
 constexpr float kRescaleThreshold = 8.f;
 
@@ -67,7 +69,7 @@ struct Cfg {
 };
 
 template <int D, int FMT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1)  // D = 64: two CTAs per SM, 88 registers
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, AttnParams p) {
   using T = typename std::conditional<FMT == 0, __half, __nv_bfloat16>::type;
@@ -96,6 +98,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   int* s_count = reinterpret_cast<int*>(tmem_holder + 1);
   int* s_range = s_count + 1;                // [2]
 
+  __shared__ float s_xchg[2][2][kTileM];  // [step parity][K block of the pair][row]: row maxima of the two threads of a row
+  __shared__ float s_lsum[2][kTileM];     // their partial row sums, at the end
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.x, tile = blockIdx.y;
   const int br0 = tile * 2;
@@ -106,19 +110,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     mbar_init(q_full, 1);
     for (int s = 0; s < kKStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
     for (int s = 0; s < kVStages; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-    for (int s = 0; s < kSBuf; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4); }
-    mbar_init(p_full, 4);
+    for (int s = 0; s < kSBuf; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], kSoftmaxWarps); }
+    mbar_init(p_full, kSoftmaxWarps);
     mbar_init(pv_done, 1);
     fence_mbar_init();
     s_range[0] = p.row_ptr[br0];
     s_range[1] = p.row_ptr[br0 + 2];
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == kWarpLoad && lane == 0) {
     prefetch_tensormap(&tm_q);
     prefetch_tensormap(&tm_k);
     prefetch_tensormap(&tm_v);
   }
-  if (warp == 5) tmem_alloc<C::kTmemCols>(tmem_holder);
+  if (warp == kWarpQK) tmem_alloc<C::kTmemCols>(tmem_holder);
   for (int k = threadIdx.x; k < ncb; k += kThreads) kmask[k] = 0;
   __syncthreads();
   // the two block rows are consecutive in the BCSR array: entry = (block row << 16) | K block
@@ -149,7 +153,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const long long kv_row0 = (long long)head * p.Ns;
 
   bool failed = false;  // a bounded wait of this thread gave up
-  if (warp == 4) {
+  if (warp == kWarpLoad) {
     // ------------------------------ producer ------------------------------
     if (lane == 0 && count > 0) {
       mbar_arrive_expect_tx(q_full, C::kQBytes);
@@ -179,7 +183,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       failed |= !ok;
       if (!ok) atomicExch(&p.status[0], 1);
     }
-  } else if (warp == 5) {
+  } else if (warp == kWarpQK) {
     // ------------------------------ S = Q K^T ------------------------------
     const uint64_t desc_hi = make_smem_desc(0, 16, 1024, SW_128B);
     const uint32_t q_lo = smem_u32(q_s) >> 4, k_lo = smem_u32(k_s) >> 4;
@@ -205,7 +209,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
     failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[1], 1);
-  } else if (warp == 6) {
+  } else if (warp == kWarpPV) {
     // ------------------------------ O += P V ------------------------------
     // P: K-major, two 64-key chunks of [128 rows x 128 B]; V: MN-major (head dim contiguous), 8 keys
     // per 1024-byte group, 64-element chunks of the head dim kPair * 128 bytes apart.
@@ -235,46 +239,62 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[2], 1);
   } else {
-    // ------------------------------ softmax + epilogue (warps 0-3) ------------------------------
-    const int row = warp * 32 + lane;          // row of the Q tile == TMEM lane
+    // ------------------------------ softmax + epilogue (warps 0-7) ------------------------------
+    // Two threads per row: warp w and warp w + 4 share a tensor-memory lane quadrant; the first takes
+    // the first K block of a pair (score columns 0-63), the second the other one.  They exchange their
+    // row maxima through shared memory once per step, keep partial row sums, and split the columns of O
+    // when it is rescaled or written out.  A single warp runs this instruction stream at one
+    // instruction per several cycles, and it sits in the chain QK^T -> softmax -> P V of every step.
+    // Every thread passes the same named barriers whatever happens: after a wait has given up it only
+    // keeps the barrier count.
+    const int quad = warp & 3, colhalf = warp >> 2;
+    const int row = quad * 32 + lane;          // row of the Q tile == TMEM lane
     const int half = row >> 6;                 // which of the two block rows
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const long long grow = (long long)tile * kTileM + row;  // row inside the head
+    constexpr int kOChunks = D / 64;           // 32-column chunks of O per thread
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int j = 0; j < npairs && ok; ++j) {
+    for (int j = 0; j < npairs; ++j) {
       const int nblk = min(2, count - 2 * j);
       const int sb = j % kSBuf;
-      const int e0 = ulist[2 * j], e1 = nblk > 1 ? ulist[2 * j + 1] : 0;
-      const bool have0 = (e0 >> half) & 1, have1 = (e1 >> half) & 1;
-      const int kb[2] = {e0 >> 2, e1 >> 2};
-      const bool have[2] = {have0, have1};
-      if (!mbar_wait_warp(&s_full[sb], (j / kSBuf) & 1)) { ok = false; break; }
-      tc_fence_after_sync();
-      const uint32_t s_addr = tmem_base + lane_base + sb * kPair;
-      // ---- pass 1: row maximum over the kept, unmasked scores ----
+      const int e = colhalf < nblk ? ulist[2 * j + colhalf] : 0;
+      const bool mine = (e >> half) & 1;       // this thread's block is kept in its block row (warp-uniform)
+      const int kb = e >> 2;
+      const uint32_t s_addr = tmem_base + lane_base + sb * kPair + colhalf * kBlk;
+      // ---- pass 1: row maximum over the kept, unmasked scores of this thread's block ----
       float mx = -INFINITY;
-      for (int b = 0; b < nblk; ++b) {
-        if (!have[b]) continue;  // warp-uniform: a warp lies inside one block row
+      if (ok) {
+        if (!mbar_wait_warp(&s_full[sb], (j / kSBuf) & 1)) {
+          ok = false;
+        } else {
+          tc_fence_after_sync();
+          if (mine) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t r[32];
-          tmem_ld_x32(s_addr + b * kBlk + h * 32, r);
-          tmem_ld_wait();
-          if (p.mask) {
-            const uint8_t* mrow = p.mask + grow * p.Ns + (long long)kb[b] * kBlk + h * 32;
-            const uint4 m0 = __ldg(reinterpret_cast<const uint4*>(mrow));
-            const uint4 m1 = __ldg(reinterpret_cast<const uint4*>(mrow) + 1);
-            const uint32_t mw[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+            for (int h = 0; h < 2; ++h) {
+              uint32_t r[32];
+              tmem_ld_x32(s_addr + h * 32, r);
+              tmem_ld_wait();
+              if (p.mask) {
+                const uint8_t* mrow = p.mask + grow * p.Ns + (long long)kb * kBlk + h * 32;
+                const uint4 m0 = __ldg(reinterpret_cast<const uint4*>(mrow));
+                const uint4 m1 = __ldg(reinterpret_cast<const uint4*>(mrow) + 1);
+                const uint32_t mw[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if ((mw[i >> 2] >> (8 * (i & 3))) & 0xffu) mx = fmaxf(mx, __uint_as_float(r[i]));
-          } else {
+                for (int i = 0; i < 32; ++i)
+                  if ((mw[i >> 2] >> (8 * (i & 3))) & 0xffu) mx = fmaxf(mx, __uint_as_float(r[i]));
+              } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+              }
+            }
           }
         }
       }
+      s_xchg[j & 1][colhalf][row] = mx;
+      named_barrier_sync(1, kSoftmaxWarps * 32);
+      if (!ok) continue;
+      mx = fmaxf(mx, s_xchg[j & 1][colhalf ^ 1][row]);
       const float m_new = mx * p.scale_log2;  // scale > 0
       // ---- lazy rescale of the running state ----
       float alpha = 1.f;
@@ -284,11 +304,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         l_run *= alpha;
       }
       // previous P V must be finished before P is overwritten or O is rescaled
-      if (j > 0 && !mbar_wait_warp(pv_done, (j - 1) & 1)) { ok = false; break; }
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+      if (j > 0 && !mbar_wait_warp(pv_done, (j - 1) & 1)) { ok = false; continue; }
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {  // the partner warp sees the same alphas and takes the other columns
         tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = colhalf * kOChunks; c < (colhalf + 1) * kOChunks; ++c) {
           uint32_t r[32];
           tmem_ld_x32(tmem_base + lane_base + C::kOCol + c * 32, r);
           tmem_ld_wait();
@@ -299,20 +319,20 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tmem_st_wait();
       }
       // ---- pass 2: P = exp2(S * scale * log2e - m) -> shared memory (K-major, 128-byte swizzle) ----
-      for (int b = 0; b < nblk; ++b) {
-        uint8_t* prow = p_s + b * (kTileM * 128) + row * 128;
+      if (colhalf < nblk) {  // this thread's block of the pair
+        uint8_t* prow = p_s + colhalf * (kTileM * 128) + row * 128;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           uint32_t packed[16];
-          if (have[b]) {  // warp-uniform: tcgen05.ld needs the whole warp
+          if (mine) {  // warp-uniform: tcgen05.ld needs the whole warp
             uint32_t r[32];
-            tmem_ld_x32(s_addr + b * kBlk + h * 32, r);
+            tmem_ld_x32(s_addr + h * 32, r);
             tmem_ld_wait();
             // every score of this row masked so far: subtracting +inf makes every probability zero
             const float neg_m = m_run > -INFINITY ? -m_run : -INFINITY;
             uint32_t mw[8];
             if (p.mask) {
-              const uint8_t* mrow = p.mask + grow * p.Ns + (long long)kb[b] * kBlk + h * 32;
+              const uint8_t* mrow = p.mask + grow * p.Ns + (long long)kb * kBlk + h * 32;
               const uint4 m0 = __ldg(reinterpret_cast<const uint4*>(mrow));
               const uint4 m1 = __ldg(reinterpret_cast<const uint4*>(mrow) + 1);
               mw[0] = m0.x; mw[1] = m0.y; mw[2] = m0.z; mw[3] = m0.w;
@@ -366,10 +386,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[3], 1);
     tc_fence_after_sync();
+    s_lsum[colhalf][row] = l_run;  // the row sum is the two threads' partial sums
+    named_barrier_sync(1, kSoftmaxWarps * 32);
+    l_run += s_lsum[colhalf ^ 1][row];
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
     T* orow = static_cast<T*>(p.O) + (q_row0 + row) * D;
 #pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = colhalf * kOChunks; c < (colhalf + 1) * kOChunks; ++c) {
       uint32_t r[32];
       if (npairs > 0 && ok) {
         tmem_ld_x32(tmem_base + lane_base + C::kOCol + c * 32, r);
@@ -395,14 +418,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       for (int q = 0; q < 4; ++q)
         dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
     }
-    if (p.lse) {
+    if (p.lse && colhalf == 0) {
       // natural-log sum of exponentials of the scaled scores (-inf for a fully masked row)
       p.lse[(long long)head * p.Nt + grow] = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
     }
   }
   tc_fence_before_sync();
   sync_and_drain(failed);
-  if (warp == 5) {
+  if (warp == kWarpQK) {
     tc_fence_after_sync();
     tmem_dealloc<C::kTmemCols>(tmem_base);
   }
