@@ -238,6 +238,32 @@ def run_extras(device, peaks, flush, only=None):
     except Exception as e:
         extras['attention_b4h16s4096d64'] = {'error': repr(e)[:200]}
 
+    # stand-alone SparseSoftmax forward on compressed scores of the same attention mask (the fused kernel
+    # above never materialises them; this is the operator the unfused composition and the API expose)
+    try:
+        if not want('softmax'):
+            raise KeyError('skipped')
+        heads, S = 64, 4096
+        amask = oracle.band_global_random_mask(S, S, 64, 8, 0.05, seed=0).to(device)
+        sop = sparta.nn.SparseSoftmax(amask, 8.0, compressed=True)
+        dg = torch.Generator(device=device).manual_seed(7)
+        xd = torch.randn((heads, S, S), generator=dg, device=device, dtype=torch.float16)
+        sop.build({'forward:y': {'_impl': 'sparta', 'BLOCK_SIZE_H_VALUE': 64, 'BLOCK_SIZE_W_VALUE': 64,
+                                 'ROW_TILE_VALUE': 4}}, sample_inputs=[xd])
+        six = sop.get_sparse_indexes('y')
+        xc = six.convert(xd)
+        del xd
+        nnz = six.block_nnz
+        nbytes = 2.0 * heads * nnz * 64 * 64 * 2  # read x + write y, kept blocks only (1.35 GB: larger than L2)
+        with torch.no_grad():
+            ms = time_steps(lambda: sop(xc), 5, 3, lambda: None) / 5
+        extras['softmax_b4h16s4096_compressed'] = {
+            'fwd_ms': round(ms, 4), 'nnz_blocks': nnz, 'gbs': round(nbytes / ms / 1e6, 1),
+            'frac_hbm_peak': round(nbytes / ms / 1e6 / peaks['hbm_gbs'], 4), 'l2': 'operands (1.35 GB) larger than L2, no flush'}
+        del xc, sop
+    except Exception as e:
+        extras['softmax_b4h16s4096_compressed'] = {'error': repr(e)[:200]}
+
     # the large attention configuration: bf16, 64 x 32 = 2048 heads, S 8192, D 128 (17 GB of q, k, v, o),
     # same mask generator on a 128 x 128 grid of 64 x 64 blocks; one GPU holds all heads here, the
     # multi-GPU form shards the head dimension with no exchange
@@ -369,7 +395,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-extras', action='store_true')
     ap.add_argument('--extras', default=None,
-                    help='comma list of extra measurements to run: linear,attention,attention_large,convert,readme (default all)')
+                    help='comma list of extra measurements to run: linear,attention,softmax,attention_large,convert,readme (default all)')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
 

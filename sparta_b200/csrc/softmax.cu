@@ -1,5 +1,6 @@
-// Masked softmax over the kept blocks of each row: one warp per matrix row, one online
-// (max, sum) pass followed by one write pass, so x is read from HBM once (the second read hits L1/L2).
+// Masked softmax over the kept blocks of each row, one warp per matrix row.  softmax_kernel: one online
+// (max, sum) pass followed by one write pass, so x is read from HBM once (the second read hits L1/L2);
+// softmax_fwd_vec_kernel: the forward pass with the row held in registers (16-byte accesses).
 //
 // Replaces sparta_sparse_softmax_forward.cuh.j2 / sparta_sparse_softmax_backward.cuh.j2
 // (sparta/specializer/kernels/templates/): three global passes plus a per-thread index list there.
@@ -80,9 +81,136 @@ __global__ void __launch_bounds__(256) softmax_kernel(SmParams p) {
   }
 }
 
+// Forward pass with 16-byte accesses for rows that fit in registers: a lane holds up to kVecs vectors of
+// the row (2048 sixteen-bit or 1024 fp32 values per row), all requested before the first is used, so
+// x is read once and every value is exponentiated once (ex2 on values pre-scaled by log2 e).  Longer
+// rows take the scalar two-pass path of softmax_kernel inside the same launch.  The host checks the
+// alignment this needs (block width a multiple of the vector, 16-byte aligned bases and rows).
+constexpr int kVecs = 8;
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(SmParams p) {
+  constexpr int E = 16 / sizeof(T);
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= p.H) return;
+  const long long bstride = p.compressed ? p.val_stride_blocks * p.BH * p.BW : (long long)p.H * p.W;
+  const T* x = static_cast<const T*>(p.x) + (long long)blockIdx.y * bstride;
+  T* out = static_cast<T*>(p.out) + (long long)blockIdx.y * bstride;
+  const int br = row / p.BH, y = row - br * p.BH;
+  const int t0 = p.row_ptr[br], t1 = p.row_ptr[br + 1];
+  const int n = (t1 - t0) * p.BW;
+  const int shift = __ffs(p.BW) - 1;  // BW is a power of two
+  const int nv = n / E;
+  if (nv > 32 * kVecs) {  // row too long for the registers: scalar path (warp-uniform branch)
+    float m = -INFINITY, s = 0.f;
+    for (int j = lane; j < n; j += 32) {
+      const long long o = elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1));
+      if (p.mask && !p.mask[o]) continue;
+      const float v = to_float(x[o]) * p.scale;
+      if (v > m) { s = s * expf(m - v) + 1.f; m = v; }
+      else s += expf(v - m);
+    }
+    const float mw = warp_max(m);
+    s = (m == -INFINITY) ? 0.f : s * expf(m - mw);
+    s = warp_sum(s);
+    const float inv = s > 0.f ? 1.f / s : 0.f;
+    for (int j = lane; j < n; j += 32) {
+      const long long o = elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1));
+      float r = 0.f;
+      if (!p.mask || p.mask[o]) r = expf(to_float(x[o]) * p.scale - mw) * inv;
+      out[o] = from_float<T>(r);
+    }
+    return;
+  }
+  const float scale2 = p.scale * 1.4426950408889634f;
+  long long off[kVecs];
+  uint4 raw[kVecs];  // the row's values stay packed in their own type: 32 registers, so four CTAs fit an SM
+#pragma unroll
+  for (int i = 0; i < kVecs; ++i) {
+    const int j = (lane + 32 * i) * E;
+    if (j < n) {
+      off[i] = elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1));
+      raw[i] = *reinterpret_cast<const uint4*>(x + off[i]);
+    }
+  }
+  // pass 1: maximum; masked elements become -inf in place, so the later passes need no mask
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kVecs; ++i) {
+    if ((lane + 32 * i) * E < n) {
+      T* e = reinterpret_cast<T*>(&raw[i]);
+      unsigned long long mk = ~0ull;  // E mask bytes
+      if (p.mask) {
+        if (E == 8) mk = *reinterpret_cast<const unsigned long long*>(p.mask + off[i]);
+        else mk = *reinterpret_cast<const unsigned int*>(p.mask + off[i]);
+      }
+#pragma unroll
+      for (int k = 0; k < E; ++k) {
+        if (!((mk >> (8 * k)) & 0xffull)) e[k] = from_float<T>(-INFINITY);
+        m = fmaxf(m, to_float(e[k]));
+      }
+    }
+  }
+  const float mw = warp_max(m) * scale2;                // scale > 0
+  const float sub = mw > -INFINITY ? mw : 0.f;          // a fully masked row: every value is -inf, every probability 0
+  // pass 2: unnormalised probabilities, stored back in the row's own type; the sum takes the fp32 values
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < kVecs; ++i) {
+    if ((lane + 32 * i) * E < n) {
+      T* e = reinterpret_cast<T*>(&raw[i]);
+#pragma unroll
+      for (int k = 0; k < E; ++k) {
+        const float pe = ex2_approx(fmaf(to_float(e[k]), scale2, -sub));
+        s += pe;
+        e[k] = from_float<T>(pe);
+      }
+    }
+  }
+  s = warp_sum(s);
+  const float inv = s > 0.f ? 1.f / s : 0.f;
+#pragma unroll
+  for (int i = 0; i < kVecs; ++i) {
+    if ((lane + 32 * i) * E < n) {
+      T* e = reinterpret_cast<T*>(&raw[i]);
+#pragma unroll
+      for (int k = 0; k < E; ++k) e[k] = from_float<T>(to_float(e[k]) * inv);
+      *reinterpret_cast<uint4*>(out + off[i]) = raw[i];
+    }
+  }
+}
+
+// whether the 16-byte path applies: block width and row pitch multiples of the vector, aligned bases
+bool vec_ok(const SmParams& p, int dtype) {
+  const int esz = dtype == SPARTA_F32 ? 4 : 2, E = 16 / esz;
+  if (p.BW % E || !(p.scale > 0.f)) return false;  // the kernel scales the row maximum after taking it
+  if ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.out)) & 15) return false;
+  if (p.mask && (reinterpret_cast<uintptr_t>(p.mask) & 7)) return false;
+  const long long bstride = p.compressed ? p.val_stride_blocks * p.BH * p.BW : (long long)p.H * p.W;
+  if (bstride % E) return false;
+  if (!p.compressed && p.W % E) return false;
+  return true;
+}
+
 template <bool BACKWARD>
 int launch(const SmParams& p, int batch, int dtype, cudaStream_t st) {
   dim3 grid((p.H + 7) / 8, batch), block(256);
+  if (!BACKWARD && vec_ok(p, dtype)) {
+    switch (dtype) {
+      case SPARTA_F32: softmax_fwd_vec_kernel<float><<<grid, block, 0, st>>>(p); break;
+      case SPARTA_F16: softmax_fwd_vec_kernel<__half><<<grid, block, 0, st>>>(p); break;
+      case SPARTA_BF16: softmax_fwd_vec_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(p); break;
+      default: return SPARTA_ERR_BAD_ARG;
+    }
+    return launch_status();
+  }
   switch (dtype) {
     case SPARTA_F32: softmax_kernel<float, BACKWARD><<<grid, block, 0, st>>>(p); break;
     case SPARTA_F16: softmax_kernel<__half, BACKWARD><<<grid, block, 0, st>>>(p); break;
