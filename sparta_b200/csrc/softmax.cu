@@ -4,6 +4,8 @@
 //
 // Replaces sparta_sparse_softmax_forward.cuh.j2 / sparta_sparse_softmax_backward.cuh.j2
 // (sparta/specializer/kernels/templates/): three global passes plus a per-thread index list there.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace sparta {
@@ -94,6 +96,21 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// Two 16-bit values at a time: a register of the row vector holds a pair, and the pair forms of max,
+// multiply and conversion keep the instruction count per value low (element-wise access to the packed
+// registers cost a byte-permute per value and made the kernel issue-bound at 24 instructions per value).
+template <typename T> struct Pair;
+template <> struct Pair<__half> {
+  using P = __half2;
+  static __device__ __forceinline__ float2 unpack(P v) { return __half22float2(v); }
+  static __device__ __forceinline__ P pack(float a, float b) { return __floats2half2_rn(a, b); }
+};
+template <> struct Pair<__nv_bfloat16> {
+  using P = __nv_bfloat162;
+  static __device__ __forceinline__ float2 unpack(P v) { return __bfloat1622float2(v); }
+  static __device__ __forceinline__ P pack(float a, float b) { return __floats2bfloat162_rn(a, b); }
+};
+
 template <typename T>
 __global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(SmParams p) {
   constexpr int E = 16 / sizeof(T);
@@ -146,15 +163,23 @@ __global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(SmParams p) {
   for (int i = 0; i < kVecs; ++i) {
     if ((lane + 32 * i) * E < n) {
       T* e = reinterpret_cast<T*>(&raw[i]);
-      unsigned long long mk = ~0ull;  // E mask bytes
       if (p.mask) {
+        unsigned long long mk;  // E mask bytes
         if (E == 8) mk = *reinterpret_cast<const unsigned long long*>(p.mask + off[i]);
         else mk = *reinterpret_cast<const unsigned int*>(p.mask + off[i]);
-      }
 #pragma unroll
-      for (int k = 0; k < E; ++k) {
-        if (!((mk >> (8 * k)) & 0xffull)) e[k] = from_float<T>(-INFINITY);
-        m = fmaxf(m, to_float(e[k]));
+        for (int k = 0; k < E; ++k)
+          if (!((mk >> (8 * k)) & 0xffull)) e[k] = from_float<T>(-INFINITY);
+      }
+      if constexpr (sizeof(T) == 2) {
+        using PT = typename Pair<T>::P;
+        const PT* h = reinterpret_cast<const PT*>(&raw[i]);
+        const PT mm = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));  // exact in any precision
+        const float2 f = Pair<T>::unpack(mm);
+        m = fmaxf(m, fmaxf(f.x, f.y));
+      } else {
+#pragma unroll
+        for (int k = 0; k < E; ++k) m = fmaxf(m, to_float(e[k]));
       }
     }
   }
@@ -165,12 +190,24 @@ __global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(SmParams p) {
 #pragma unroll
   for (int i = 0; i < kVecs; ++i) {
     if ((lane + 32 * i) * E < n) {
-      T* e = reinterpret_cast<T*>(&raw[i]);
+      if constexpr (sizeof(T) == 2) {
+        using PT = typename Pair<T>::P;
+        PT* h = reinterpret_cast<PT*>(&raw[i]);
 #pragma unroll
-      for (int k = 0; k < E; ++k) {
-        const float pe = ex2_approx(fmaf(to_float(e[k]), scale2, -sub));
-        s += pe;
-        e[k] = from_float<T>(pe);
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = Pair<T>::unpack(h[k]);
+          const float p0 = ex2_approx(fmaf(f.x, scale2, -sub)), p1 = ex2_approx(fmaf(f.y, scale2, -sub));
+          s += p0 + p1;
+          h[k] = Pair<T>::pack(p0, p1);
+        }
+      } else {
+        T* e = reinterpret_cast<T*>(&raw[i]);
+#pragma unroll
+        for (int k = 0; k < E; ++k) {
+          const float pe = ex2_approx(fmaf(to_float(e[k]), scale2, -sub));
+          s += pe;
+          e[k] = from_float<T>(pe);
+        }
       }
     }
   }
@@ -179,9 +216,26 @@ __global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(SmParams p) {
 #pragma unroll
   for (int i = 0; i < kVecs; ++i) {
     if ((lane + 32 * i) * E < n) {
-      T* e = reinterpret_cast<T*>(&raw[i]);
+      if constexpr (sizeof(T) == 2) {
+        // fp16: 1 / sum lies in [1 / 2048, 1], exact enough in the row's own type: one multiply per pair
+        using PT = typename Pair<T>::P;
+        PT* h = reinterpret_cast<PT*>(&raw[i]);
+        if constexpr (std::is_same<T, __half>::value) {
+          const PT inv2 = Pair<T>::pack(inv, inv);
 #pragma unroll
-      for (int k = 0; k < E; ++k) e[k] = from_float<T>(to_float(e[k]) * inv);
+          for (int k = 0; k < 4; ++k) h[k] = __hmul2(h[k], inv2);
+        } else {  // bf16 keeps only eight bits: multiply in fp32
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 f = Pair<T>::unpack(h[k]);
+            h[k] = Pair<T>::pack(f.x * inv, f.y * inv);
+          }
+        }
+      } else {
+        T* e = reinterpret_cast<T*>(&raw[i]);
+#pragma unroll
+        for (int k = 0; k < E; ++k) e[k] = from_float<T>(to_float(e[k]) * inv);
+      }
       *reinterpret_cast<uint4*>(out + off[i]) = raw[i];
     }
   }
