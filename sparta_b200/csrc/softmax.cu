@@ -112,7 +112,7 @@ template <> struct Pair<__nv_bfloat16> {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(SmParams p) {
+__global__ void __launch_bounds__(128, 9) softmax_fwd_vec_kernel(SmParams p) {
   constexpr int E = 16 / sizeof(T);
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -147,13 +147,13 @@ __global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(SmParams p) {
     return;
   }
   const float scale2 = p.scale * 1.4426950408889634f;
-  long long off[kVecs];
+  uint32_t off[kVecs];  // within one batch slice (the host checks that a slice has fewer than 2^32 elements)
   uint4 raw[kVecs];  // the row's values stay packed in their own type: 32 registers, so four CTAs fit an SM
 #pragma unroll
   for (int i = 0; i < kVecs; ++i) {
     const int j = (lane + 32 * i) * E;
     if (j < n) {
-      off[i] = elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1));
+      off[i] = static_cast<uint32_t>(elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1)));
       raw[i] = *reinterpret_cast<const uint4*>(x + off[i]);
     }
   }
@@ -248,7 +248,7 @@ bool vec_ok(const SmParams& p, int dtype) {
   if ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.out)) & 15) return false;
   if (p.mask && (reinterpret_cast<uintptr_t>(p.mask) & 7)) return false;
   const long long bstride = p.compressed ? p.val_stride_blocks * p.BH * p.BW : (long long)p.H * p.W;
-  if (bstride % E) return false;
+  if (bstride % E || bstride >= (1ll << 32)) return false;
   if (!p.compressed && p.W % E) return false;
   return true;
 }
