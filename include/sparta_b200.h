@@ -193,6 +193,8 @@ int sparta_bsmm_dds(const sparta_bsmm_args* args, void* stream);
  * x, y, (dy, dx): [batch, H, W] (compressed = 0) or [batch, val_stride_blocks*BH*BW] (compressed = 1);
  * mask: uint8 in the same layout as x (one copy, shared by the batch) or NULL = every element of
  * a kept block takes part.  Masked elements and, for compressed = 0, dropped blocks are written 0.
+ * With compressed = 0 the output is zero-filled before the kernel runs, so it must not alias an input
+ * (SPARTA_ERR_BAD_ARG); compressed tensors may be processed in place.
  */
 int sparta_softmax_fwd(const void* x, void* y, const int32_t* row_ptr, const int32_t* bcsr_idx,
                        const int32_t* nnz, const uint8_t* mask, float scale, int batch, int H, int W,
@@ -237,7 +239,10 @@ int sparta_tile_table(int op, int dtype, sparta_tile_entry* out_entries, int max
 
 /* Status words of the tcgen05 kernels on the current device: all zero unless a bounded wait (on an
  * mbarrier) ran out, in which case the kernel stopped early and its output is invalid.  Word 0:
- * producer, 1: MMA issuer, 2: epilogue, 3: reserved.  Synchronises the device and clears the words.
+ * a producer (TMA-issuing) warp gave up, 1: an MMA-issuing warp, 2: the wait for the accumulator before
+ * the epilogue (in the fused attention: the P.V issuer), 3: the warps between the two (the dsd kernel's
+ * activation converters, the attention kernel's softmax warps).  Synchronises the device and clears the
+ * words.
  * No counterpart in the reference, whose kernels contain no waits. */
 int sparta_last_status(int32_t h_out[4]);
 

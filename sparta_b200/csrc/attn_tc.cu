@@ -128,8 +128,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   // the two block rows are consecutive in the BCSR array: entry = (block row << 16) | K block
   for (int e = s_range[0] + threadIdx.x; e < s_range[1]; e += kThreads) {
     const int v = __ldg(p.idx + e);
-    atomicOr(reinterpret_cast<unsigned int*>(kmask + ((v & 0xffff) & ~3)),
-             (1u << ((v >> 16) - br0)) << (8 * ((v & 0xffff) & 3)));
+    const int kb = v & 0xffff, r = (v >> 16) - br0;
+    if (kb < ncb && r >= 0 && r < 2)  // index arrays come from the caller: never index shared memory with them unchecked
+      atomicOr(reinterpret_cast<unsigned int*>(kmask + (kb & ~3)), (1u << r) << (8 * (kb & 3)));
   }
   __syncthreads();
   if (warp == 0) {  // ordered compaction of the merged list
@@ -451,12 +452,8 @@ int launch_attn(const void* Q, const void* K, const void* V, const AttnParams& p
     if (rc != SPARTA_OK) return rc;
   }
   auto kern = attn_fwd_tc_kernel<D, FMT>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
-  }
+  static SmemAttrOnce attr;
+  if (cudaError_t e = attr.ensure(kern, C::kSmem); e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(p.heads, p.Nt / kTileM);  // x = head: the heavy first tile of every head is scheduled first
   kern<<<grid, kThreads, C::kSmem, st>>>(tm_q, tm_k, tm_v, p);
   return launch_status();

@@ -507,13 +507,8 @@ extern "C" int sparta_bcs_build(const uint8_t* mask, int n_masks, int H, int W, 
     const uint32_t box[2] = {kTileCols / 4, kTileRows};
     if (tc::make_tensor_map(&tm, mask, tc::kTensorMapU32, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE) ==
         SPARTA_OK) {
-      static bool attr_set = false;
-      if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(bcs_build_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kTmaSmem);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        attr_set = true;
-      }
+      static SmemAttrOnce attr;
+      if (cudaError_t e = attr.ensure(bcs_build_tma_kernel, kTmaSmem); e != cudaSuccess) return static_cast<int>(e);
       const int units = R * ((W + kTileCols - 1) / kTileCols);
       int per_mask = (2 * kNumSMs) / n_masks;                       // fill the 296 CTA slots once
       const int by_units = (units + kTmaWarps - 1) / kTmaWarps;     // at least one unit per warp

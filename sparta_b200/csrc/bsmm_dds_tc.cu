@@ -85,8 +85,9 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   __syncthreads();
   for (int e = s_range[0] + threadIdx.x; e < s_range[1]; e += kThreads) {
     const int v = __ldg(idx + e);
-    const int c = v & 0xffff;
-    atomicOr(reinterpret_cast<unsigned int*>(cmask + (c & ~3)), (1u << ((v >> 16) - mb0)) << (8 * (c & 3)));
+    const int c = v & 0xffff, r = (v >> 16) - mb0;
+    if (c < p.Nb && r >= 0 && r < 4)  // index arrays come from the caller: never index shared memory with them unchecked
+      atomicOr(reinterpret_cast<unsigned int*>(cmask + (c & ~3)), (1u << r) << (8 * (c & 3)));
   }
   __syncthreads();
   if (warp == 0) {
@@ -187,9 +188,10 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     named_barrier_sync(1, 128);
     for (int e = s_range[0] + threadIdx.x; e < s_range[1]; e += 128) {
       const int v = __ldg(idx + e);
-      const int c = v & 0xffff;
+      const int c = v & 0xffff, r = (v >> 16) - mb0;
+      if (r < 0 || r >= 4) continue;
       for (int l = 0; l < ncols; ++l)
-        if (clist[c_first + l] == c) s_pos[((v >> 16) - mb0) * kGroup + l] = e;
+        if (clist[c_first + l] == c) s_pos[r * kGroup + l] = e;
     }
     named_barrier_sync(1, 128);
     if (!mbar_wait_warp(accum_bar, LOOP ? (it & 1) : 0)) {
@@ -282,16 +284,11 @@ int launch_dds(const BsmmParams& p, cudaStream_t st) {
   q.status = device_status_ptr();
   if (!q.status) return SPARTA_ERR_DRIVER;
   constexpr int kSmem = smem_bytes(STAGES);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(bsmm_dds_tc_kernel<FMT, STAGES, false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(bsmm_dds_tc_kernel<FMT, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               kSmem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
-  }
+  static SmemAttrOnce attr_one, attr_loop;
+  if (cudaError_t e = attr_one.ensure(bsmm_dds_tc_kernel<FMT, STAGES, false>, kSmem); e != cudaSuccess)
+    return static_cast<int>(e);
+  if (cudaError_t e = attr_loop.ensure(bsmm_dds_tc_kernel<FMT, STAGES, true>, kSmem); e != cudaSuccess)
+    return static_cast<int>(e);
   // CTAs per row tile: every group its own CTA when there are few row tiles; with many (batched masks)
   // most groups of a tile are empty, and a few CTAs per tile loop over the groups instead, aiming at
   // about two CTAs per resident slot

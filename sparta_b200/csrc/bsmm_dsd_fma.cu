@@ -220,12 +220,8 @@ template <int B, int TM, typename T>
 int launch_tm(const BsmmParams& p, int panels, cudaStream_t st) {
   using S = FmaSmem<TM, T>;
   auto kern = bsmm_dsd_fma_kernel<B, TM, T>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
-  }
+  static SmemAttrOnce attr;
+  if (cudaError_t e = attr.ensure(kern, S::kTotal); e != cudaSuccess) return static_cast<int>(e);
   kern<<<dim3(panels, p.M / TM, p.batch), 2 * TM, S::kTotal, st>>>(p);
   return launch_status();
 }

@@ -580,12 +580,8 @@ int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
   q.status = device_status_ptr();
   if (!q.status) return SPARTA_ERR_DRIVER;
   auto kern = bsmm_dsd_tc_kernel<FMT, NP>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
-  }
+  static SmemAttrOnce attr;
+  if (cudaError_t e = attr.ensure(kern, kSmemTotal); e != cudaSuccess) return static_cast<int>(e);
   dim3 grid((q.Nb + NP - 1) / NP, p.M / kTileM, p.batch);
   kern<<<grid, kThreads, kSmemTotal, st>>>(tm_x, tm_w, tm_c, q);
   return launch_status();

@@ -73,7 +73,8 @@ __global__ void __launch_bounds__(kThreads) bsmm_simt_kernel(BsmmParams p) {
 
   const int out_first = p.mode == MODE_DDS ? blockIdx.x : 0;
   const int out_step = p.mode == MODE_DDS ? gridDim.x : 1;
-  const int out_last = p.mode == MODE_DDS ? nnz : 1;
+  // dds: never past the compressed output buffer (an index build with too small a capacity reports the full count)
+  const int out_last = p.mode == MODE_DDS ? ((c_comp && vstride > 0 && nnz > vstride) ? (int)vstride : nnz) : 1;
 
   for (int ob = out_first; ob < out_last; ob += out_step) {
     int by, bx, c_pos = ob;

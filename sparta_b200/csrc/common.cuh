@@ -6,6 +6,8 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/sparta_b200.h"
 
 namespace sparta {
@@ -16,6 +18,27 @@ inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? SPARTA_OK : static_cast<int>(e);
 }
+
+// A kernel's dynamic shared memory limit is an attribute of the (kernel, device) pair, so a process that
+// drives several GPUs has to set it on each of them.  One instance per kernel instantiation; the table
+// is filled under a mutex because launches may come from several host threads.
+constexpr int kMaxDevices = 64;
+struct SmemAttrOnce {
+  std::mutex mu;
+  bool done[kMaxDevices] = {};
+  template <typename Kernel>
+  cudaError_t ensure(Kernel kern, int bytes) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const bool tracked = dev >= 0 && dev < kMaxDevices;
+    std::lock_guard<std::mutex> guard(mu);
+    if (tracked && done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && tracked) done[dev] = true;
+    return e;
+  }
+};
 
 inline bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 

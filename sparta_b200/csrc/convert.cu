@@ -27,7 +27,8 @@ __device__ __forceinline__ void decode(const MoveParams& p, int t, int& by, int&
 // VEC = bytes moved per thread per step (16, 8, 4, 2 or 1); GATHER: dense -> vals, else vals -> dense
 template <int VEC, bool GATHER>
 __global__ void __launch_bounds__(256) bcs_move_kernel(MoveParams p) {
-  const int nnz = *p.nnz;
+  // never walk past the value buffer: an index build whose capacity was too small reports the full count
+  const int nnz = p.val_stride_blocks > 0 ? (int)min((long long)*p.nnz, p.val_stride_blocks) : *p.nnz;
   const size_t row_bytes = (size_t)p.BW * p.elem_bytes;        // bytes of one block row
   const size_t blk_bytes = row_bytes * p.BH;
   const int vec_per_row = (int)(row_bytes / VEC);
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(256) bcs_sum_kernel(const T* vals, T* out, con
   } else {
     // column sums walk every kept block and keep those of this block column
     const int bc = warp / BW, x = warp % BW;
-    const int nnz = *nnz_p;
+    const int nnz = val_stride_blocks > 0 ? (int)min((long long)*nnz_p, val_stride_blocks) : *nnz_p;
     for (int t = 0; t < nnz; ++t) {
       if ((idx[t] & 0xffff) != bc) continue;
       for (int y = lane; y < BH; y += 32) acc += to_float(v[((size_t)t * BH + y) * BW + x]);

@@ -296,6 +296,7 @@ extern "C" int sparta_softmax_fwd(const void* x, void* y, const int32_t* row_ptr
   int rc = check(x, y, row_ptr, bcsr_idx, nnz, batch, H, W, BH, BW, compressed, val_stride_blocks);
   if (rc != SPARTA_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!compressed && x == y) return SPARTA_ERR_BAD_ARG;  // the zero fill below would wipe the input
   if (!compressed) {  // dropped blocks of the dense-shaped output must read 0
     const size_t esz = dtype == SPARTA_F32 ? 4 : 2;
     cudaError_t e = cudaMemsetAsync(y, 0, (size_t)batch * H * W * esz, st);
@@ -313,6 +314,7 @@ extern "C" int sparta_softmax_bwd(const void* dy, const void* y, void* dx, const
   int rc = check(dy, dx, row_ptr, bcsr_idx, nnz, batch, H, W, BH, BW, compressed, val_stride_blocks);
   if (rc != SPARTA_OK) return rc;
   if (!y) return SPARTA_ERR_BAD_ARG;
+  if (!compressed && (dx == dy || dx == y)) return SPARTA_ERR_BAD_ARG;  // the zero fill below would wipe an input
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!compressed) {
     const size_t esz = dtype == SPARTA_F32 ? 4 : 2;

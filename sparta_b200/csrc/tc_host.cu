@@ -71,5 +71,3 @@ extern "C" int sparta_last_status(int32_t h_out[4]) {
   if (!h_out) return SPARTA_ERR_BAD_ARG;
   return sparta::tc::read_and_clear_status(h_out);
 }
-
-// debug helper: copies 64 trace words from a device pointer stored by the dsd kernel launcher

@@ -50,6 +50,11 @@ class KernelPlaceholder(object):
 
     def set_sample_inputs(self, sample_inputs: List[torch.Tensor]):
         self.sample_inputs = [x.detach() if type(x) is torch.Tensor else x for x in sample_inputs]
+        # the prebuilt tile shapes depend on the element type: tell every candidate kernel
+        dtype = next((x.dtype for x in self.sample_inputs if type(x) is torch.Tensor), None)
+        for kernel in self.possible_kernels.values():
+            if dtype is not None and hasattr(kernel, 'set_sample_dtype'):
+                kernel.set_sample_dtype(dtype)
 
     def test(self, num_warmups: int = 10, num_iters: int = 10, cuda: bool = True):
         return self.active_kernel().test(self.sample_inputs, num_warmups, num_iters, cuda)

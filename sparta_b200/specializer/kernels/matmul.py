@@ -16,7 +16,7 @@ from sparta_b200.specializer.kernels.kernel_base import KernelBase, PortConfig
 
 _FAMILY = {'auto': _lib.IMPL_AUTO, 'simt': _lib.IMPL_SIMT, 'tcgen05': _lib.IMPL_TCGEN05}
 _ENTRY = {'sdd': 'sparta_bsmm_sdd', 'dsd': 'sparta_bsmm_dsd', 'dds': 'sparta_bsmm_dds'}
-_SIMT_TILES = (8, 16, 32, 64)
+_OP_CODE = {'sdd': _lib.OP_SDD, 'dsd': _lib.OP_DSD, 'dds': _lib.OP_DDS}
 
 
 class SparseMatMulKernel(KernelBase):
@@ -34,6 +34,7 @@ class SparseMatMulKernel(KernelBase):
         self._transpose_B = transpose_B
         self._compressed = compressed
         self._family = 'auto'
+        self._sample_dtype = torch.float32  # element type the tile table is read for, see set_sample_dtype
         # which port is sparse, which tile sizes give its block shape, which index form it uses
         if mode == 'sdd':
             self._sparse_port = 'A'
@@ -72,6 +73,26 @@ class SparseMatMulKernel(KernelBase):
         self._add_parameter('TRANSPOSE_A', value=self._transpose_A)
         self._add_parameter('TRANSPOSE_B', value=self._transpose_B)
         self._add_parameter('COMPRESSED', value=self._compressed)
+
+    def set_sample_dtype(self, dtype: torch.dtype):
+        """Element type of the tensors the kernel will be tuned / run on: the prebuilt tile shapes depend
+        on it (the tcgen05 kernels take fp16 / bf16 only)."""
+        if dtype in _lib.DTYPE_CODE:
+            self._sample_dtype = dtype
+
+    def tile_shapes(self, dtype: torch.dtype = None) -> Dict[Any, int]:
+        """``{(BM, BK, BN): kernel family}`` of the library's tile table for this kernel's mode, transposes
+        and storage, preferred entries first.  This is what replaces the reference's tuned look-up table
+        (sparta/specializer/kernels/matmul.py:246-264): a configuration names a prebuilt tile."""
+        code = _lib.DTYPE_CODE[self._sample_dtype if dtype is None else dtype]
+        shapes: Dict[Any, int] = {}
+        for e in _lib.tile_table(_OP_CODE[self._mode], code):
+            if e.trans_a not in (-1, int(self._transpose_A)) or e.trans_b not in (-1, int(self._transpose_B)):
+                continue
+            if e.compressed not in (-1, int(self._compressed)):
+                continue
+            shapes.setdefault((e.block_m, e.block_k, e.block_n), e.impl)
+        return shapes
 
     def set_parameter(self, name: str, value: Any):
         if name == '_family':
@@ -213,8 +234,13 @@ class SparseMatMulKernel(KernelBase):
 
 
 class SparTASparseMatMulKernel(SparseMatMulKernel):
-    """Free tile sizes.  The search space keeps the reference's 16/32/64 choices
-    (matmul.py:230-244); 8 is accepted by ``compile`` as well.  THREAD_SIZE_* keys of reference
+    """Free tile sizes.  Where the reference searches 16/32/64 per dimension and compiles each point
+    (matmul.py:230-264), the search space here is read from the library's tile table for the dtype of
+    the sample inputs: every FMA tile (8 .. 64 per dimension, which includes the reference's choices, so
+    its saved configurations still build) plus the tcgen05 tiles that exist for this mode, e.g.
+    128 x 32 x 32 for the SparseLinear weight layout in fp16 / bf16.  A grid walk visits the product of
+    the per-dimension choices; combinations that are no table entry fail ``_check_parameters`` and count
+    as infinitely slow, like invalid points in the reference.  THREAD_SIZE_* keys of reference
     configurations are accepted and ignored: the prebuilt kernels fix their own thread tiling."""
 
     __algo__ = 'sparta'
@@ -223,14 +249,21 @@ class SparTASparseMatMulKernel(SparseMatMulKernel):
         super()._add_parameters()
         for dim in 'MKN':
             self._add_parameter(f'BLOCK_SIZE_{dim}_VALUE', is_tunable=True,
-                                search_space=TunableItemCfg('choice', [16, 32, 64]))
+                                search_space=TunableItemCfg('choice', [8, 16, 32, 64]))
             self._add_parameter(f'THREAD_SIZE_{dim}_VALUE')
+
+    def set_sample_dtype(self, dtype: torch.dtype):
+        super().set_sample_dtype(dtype)
+        shapes = list(self.tile_shapes())
+        for k, dim in enumerate('MKN'):
+            choices = sorted({shape[k] for shape in shapes})
+            self._parameters[f'BLOCK_SIZE_{dim}_VALUE'].search_space = TunableItemCfg('choice', choices)
 
     def _check_parameters(self, params: Dict[str, Any]):
         super()._check_parameters(params)
-        for d in 'MKN':
-            size = params[f'BLOCK_SIZE_{d}_VALUE']
-            assert size in _SIMT_TILES or size == 128, f'no prebuilt kernel for tile size {size}'
+        tile = tuple(params[f'BLOCK_SIZE_{d}_VALUE'] for d in 'MKN')
+        known = any(tile in self.tile_shapes(dtype) for dtype in _lib.DTYPE_CODE)
+        assert known, f'no prebuilt kernel for tile {tile[0]} x {tile[1]} x {tile[2]} in this layout'
 
 
 class OpenAISparseMatMulKernel(SparseMatMulKernel):

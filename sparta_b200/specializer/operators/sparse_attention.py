@@ -7,9 +7,11 @@ Two execution paths share the reference's API:
   that share one BCSR index set -- for every dtype and tile size, with backward;
 * the fused forward kernel (``sparta_attn_fwd``) for fp16 / bf16, E in {64, 128} and 64 x 64 tiles,
   where the score tensor never reaches global memory.  It is chosen automatically when the
-  configuration allows it (``fused='auto'``) and provides no backward.
+  configuration allows it (``fused='auto'``) and provides no backward: with ``'auto'`` a forward whose
+  inputs require gradients takes the composed path.
 """
 from typing import Any, Dict, List, Optional
+import os
 import warnings
 
 import numpy as np
@@ -61,6 +63,9 @@ class SparseAttention(OperatorBase):
         self._scale = 1.0
         self._attn_ws: Optional[torch.Tensor] = None
         self._attn_status: Optional[torch.Tensor] = None
+        #: debugging aid: read the kernel's status words after every fused forward (one device
+        #: synchronisation per call) and raise when a bounded wait gave up
+        self.check_status = os.environ.get('SPARTA_B200_CHECK_STATUS', '0') == '1'
         self.ready = False
 
     # ---- forward paths ------------------------------------------------------------------
@@ -68,7 +73,12 @@ class SparseAttention(OperatorBase):
         if self.ready and self.dynamic:
             self._sparse_port.refresh()
         if self.ready and self._use_fused:
-            return _FusedAttentionFunc.apply(self, query, key, value)
+            # the fused kernel is forward-only: with fused='auto' a call that autograd will differentiate
+            # takes the three-operator path, which the reference trains through
+            # (test/unit/test_sparse_attention.py:86-92); fused=True keeps the fused kernel and raises in backward
+            wants_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value))
+            if self._fused_request is True or not wants_grad:
+                return _FusedAttentionFunc.apply(self, query, key, value)
         qk = self._matmul_qk.forward(query, key)
         sm = self._softmax.forward(qk)
         return self._matmul_out.forward(sm, value)
@@ -96,6 +106,9 @@ class SparseAttention(OperatorBase):
                 _lib.ptr(mask), float(self._scale), heads, self._Nt, self._Ns, E, FUSED_BLOCK,
                 _lib.dtype_code(q), None, self._attn_status.data_ptr(),
                 self._attn_ws.data_ptr(), self._attn_ws.numel(), _lib.stream_ptr(q.device)), 'sparta_attn_fwd')
+        if self.check_status and any(self.fused_status()):
+            raise RuntimeError(f'fused sparse attention: a bounded wait ran out on the device, status words '
+                               f'{self.fused_status()}; the output is invalid')
         return out.reshape(shape)
 
     def fused_status(self) -> List[int]:

@@ -68,6 +68,9 @@ class BCSIndexes(TeSAIndexes):
     def _fetch(self):
         host = torch.stack([self.nnz_dev, self.uniform_dev]).cpu()
         self._nnz_host = host[0].tolist()
+        if max(self._nnz_host) > self.capacity:
+            raise RuntimeError(f'mask keeps {max(self._nnz_host)} blocks but the index arrays were built with '
+                               f'capacity {self.capacity}: rebuild with a larger capacity')
         self._block_nnz = int(max(self._nnz_host)) if self.batched else int(self._nnz_host[0])
         self._uniform = bool(host[1].min().item())
 

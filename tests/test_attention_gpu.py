@@ -141,3 +141,31 @@ def test_fused_attention_dynamic_mask():
         out = op(q.cuda(), k.cuda(), v.cuda())
         target = oracle.attention_reference(q.float(), k.float(), v.float(), mask)
         torch.testing.assert_close(out.float().cpu(), target, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_default_fused_setting_trains(dtype):
+    """fused='auto' (the default) with half-precision inputs that require gradients: the forward must take
+    the differentiable three-operator path, as the reference's operator does, and match oracle autograd."""
+    heads, S, E = 2, 256, 64
+    g = torch.Generator().manual_seed(13)
+    q, k, v = (torch.randn((heads, S, E), generator=g).to(dtype) for _ in range(3))
+    grad = torch.randn((heads, S, E), generator=g).to(dtype)
+    mask = oracle.band_global_random_mask(S, S, 64, 1, 0.1, seed=5)
+    op = SparseAttention(mask=mask.cuda())
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    op.build(config=params(64), sample_inputs=[qc, kc, vc])
+    assert op._use_fused  # the configuration is fusable: inference calls take the fused kernel
+    out = op(qc, kc, vc)
+    out.backward(grad.cuda())
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    target = oracle.attention_reference(qr, kr, vr, mask)
+    target.backward(grad.float())
+    tol = dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(out.detach().float().cpu(), target.detach(), **tol)
+    for got, want in ((qc.grad, qr.grad), (kc.grad, kr.grad), (vc.grad, vr.grad)):
+        torch.testing.assert_close(got.float().cpu(), want, **tol)
+    with torch.no_grad():
+        fused_out = op(qc, kc, vc)
+    assert op.fused_status() == [0, 0, 0, 0]
+    torch.testing.assert_close(fused_out.float().cpu(), target.detach(), **tol)

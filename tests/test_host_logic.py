@@ -71,7 +71,7 @@ def test_tune_sparse_linear_trial_count(backward):
     g = torch.zeros((128, 128))
     op = SparseLinear(dense, weight_mask=torch.ones((128, 128), dtype=torch.uint8))
     count = _count_trials(op, [x], [g] if backward else None)
-    assert count == (3 * 3 * 3 + 1) * (3 if backward else 1)
+    assert count == (4 * 4 * 4 + 1) * (3 if backward else 1)
 
 
 @pytest.mark.parametrize('backward', [False, True])
@@ -81,7 +81,7 @@ def test_tune_sparse_matmul_trial_count(backward):
     g = torch.zeros((4, 128, 128))
     op = SparseBatchMatMul(C_mask=torch.ones((128, 128), dtype=torch.uint8), transpose_B=True, compressed=True)
     count = _count_trials(op, [A, B], [g] if backward else None)
-    assert count == (3 * 3 * 3 + 1) * (3 if backward else 1)
+    assert count == (4 * 4 * 4 + 1) * (3 if backward else 1)
 
 
 @pytest.mark.parametrize('backward', [False, True])
@@ -100,9 +100,34 @@ def test_tune_sparse_attention_trial_count(backward):
     op = SparseAttention(mask=torch.ones((128, 128), dtype=torch.uint8))
     count = _count_trials(op, [q, k, v], [g] if backward else None)
     if backward:
-        assert count == (3 * 3 * 3 + 1) * 6 + (3 * 3 * 5) * 2
+        assert count == (4 * 3 * 4 + 1) * 6 + (4 * 3 * 5) * 2
     else:
-        assert count == (3 * 3 * 3 + 1) * 2 + (3 * 3 * 5) * 1
+        assert count == (4 * 3 * 4 + 1) * 2 + (4 * 3 * 5) * 1
+
+
+def test_search_space_follows_the_tile_table():
+    """The tunable block sizes are the library's prebuilt tiles for the sample dtype: fp32 sees the FMA tiles
+    only; fp16 on the SparseLinear weight layout also sees the 128 x 32 x 32 tcgen05 tile, and a
+    configuration saved by the reference (16 / 32 / 64) still passes the parameter check."""
+    from sparta_b200 import _lib
+    op = SparseLinear(torch.nn.Linear(256, 256), weight_mask=torch.ones((256, 256), dtype=torch.uint8))
+    op.set_sample_inputs([torch.zeros((256, 256))])
+    space = op.get_search_space()['forward:C']['sparta']
+    assert [space[f'BLOCK_SIZE_{d}_VALUE']._value for d in 'MKN'] == [[8, 16, 32, 64]] * 3
+    op.set_sample_inputs([torch.zeros((256, 256), dtype=torch.float16)])
+    space = op.get_search_space()['forward:C']['sparta']
+    assert space['BLOCK_SIZE_M_VALUE']._value == [8, 16, 32, 64, 128]
+    assert space['BLOCK_SIZE_K_VALUE']._value == [8, 16, 32, 64]
+    kernel = op.get_kernel_placeholders()['forward:C'].possible_kernels['sparta']
+    assert kernel.tile_shapes()[(128, 32, 32)] == _lib.IMPL_TCGEN05
+    assert next(iter(kernel.tile_shapes())) == (128, 32, 32)  # preferred entries come first
+    kernel._check_parameters({f'BLOCK_SIZE_{d}_VALUE': v for d, v in zip('MKN', (128, 32, 32))})
+    kernel._check_parameters({f'BLOCK_SIZE_{d}_VALUE': v for d, v in zip('MKN', (64, 16, 32))})
+    with pytest.raises(AssertionError):
+        kernel._check_parameters({f'BLOCK_SIZE_{d}_VALUE': v for d, v in zip('MKN', (128, 64, 32))})
+    # the backward:A kernel of that operator is dsd with B stored [K, N]: no tcgen05 tile
+    bwd = op.get_kernel_placeholders(True)['backward:A'].possible_kernels['sparta']
+    assert all(impl == _lib.IMPL_SIMT for impl in bwd.tile_shapes(torch.float16).values())
 
 
 def test_grid_and_random_walkers():

@@ -123,3 +123,29 @@ def test_dds_tcgen05_per_batch_masks():
     ix = op.get_sparse_indexes('C')
     full = torch.bmm(A.float(), B.float())
     torch.testing.assert_close(ix.inverse(out).float().cpu(), full * masks.cpu().float(), **TOL)
+
+
+def test_tune_reaches_the_tcgen05_kernel():
+    """The three lines of the reference's README on half-precision inputs: ``tune`` walks the tile table,
+    so it can return the 128 x 32 x 32 tile, and building that result launches the tcgen05 dsd kernel."""
+    from sparta_b200.nn import SparseLinear, tune
+    g = torch.Generator().manual_seed(7)
+    dense = torch.nn.Linear(2048, 2048).half().cuda()
+    mask = oracle.block_mask((2048, 2048), (32, 32), 0.75, generator=g).cuda()
+    x = torch.randn((2048, 2048), generator=g).half().cuda()
+    sparse_linear = SparseLinear(dense, weight_mask=mask)
+    best = tune(sparse_linear, sample_inputs=[x], max_trials=10 ** 6)
+    cfg = best['root']['forward:C']
+    tile = tuple(cfg[f'BLOCK_SIZE_{d}_VALUE'] for d in 'MKN')
+    assert cfg['_impl'] == 'sparta' and tile == (128, 32, 32), cfg
+    sparse_linear.build(best['root'], sample_inputs=[x])
+    kernel = sparse_linear.get_kernel_placeholders()['forward:C'].active_kernel()
+    assert kernel.tile_shapes(torch.float16)[tile] == _lib.IMPL_TCGEN05
+    y = sparse_linear(x)
+    assert _lib.last_status() == [0, 0, 0, 0]
+    expect = torch.nn.functional.linear(x.float().cpu(), (dense.weight.float() * mask).cpu(), dense.bias.float().cpu())
+    torch.testing.assert_close(y.float().cpu(), expect, **TOL)
+    # the same tile with the family pinned gives the same bits: AUTO did dispatch to tcgen05
+    pinned = {'forward:C': {**cfg, '_family': 'tcgen05'}}
+    sparse_linear.build(pinned, sample_inputs=[x])
+    assert torch.equal(sparse_linear(x), y)
