@@ -7,7 +7,6 @@ parameters against the prebuilt tile table and binds a closure that calls the C-
 from __future__ import annotations
 
 import abc
-import dataclasses
 from typing import Any, Callable, Dict, List, Optional
 
 import torch
@@ -17,76 +16,127 @@ from sparta_b200.tesa import get_bcs_function, BCSIndexes
 from sparta_b200.testing import profile
 
 
-@dataclasses.dataclass
-class _Parameter:
-    name: str
-    value: Optional[Any] = None
-    is_tunable: bool = False
-    is_dynamic: bool = False
-    search_space: Optional[TunableItemCfg] = None
+class _ParameterTable(object):
+    """Name -> value table of a kernel with the choices of the tunable entries.  The names are the
+    configuration schema shared with the reference (``BLOCK_SIZE_M_VALUE`` ...): a configuration saved
+    by either implementation can be handed to ``compile``."""
 
-    def __post_init__(self):
-        if self.search_space is not None:
-            assert self.is_tunable
+    __slots__ = ('_values', '_spaces', '_dynamic')
+
+    def __init__(self):
+        self._values: Dict[str, Any] = {}
+        self._spaces: Dict[str, TunableItemCfg] = {}  # present <=> the parameter is tunable
+        self._dynamic: set = set()
+
+    def add(self, name: str, value: Any = None, space: Optional[TunableItemCfg] = None, dynamic: bool = False):
+        self._values[name] = value
+        if space is not None:
+            self._spaces[name] = space
+        if dynamic:
+            self._dynamic.add(name)
+
+    def __contains__(self, name: str) -> bool:
+        return name in self._values
+
+    def __getitem__(self, name: str) -> '_ParameterView':
+        return _ParameterView(self, name)
+
+    def items(self):
+        return ((name, _ParameterView(self, name)) for name in self._values)
+
+    def keys(self):
+        return self._values.keys()
 
 
-@dataclasses.dataclass
+class _ParameterView(object):
+    """One row of the table (``value``, ``is_tunable``, ``search_space``)."""
+
+    __slots__ = ('_table', 'name')
+
+    def __init__(self, table: _ParameterTable, name: str):
+        if name not in table._values:
+            raise KeyError(name)
+        self._table, self.name = table, name
+
+    @property
+    def value(self):
+        return self._table._values[self.name]
+
+    @value.setter
+    def value(self, v):
+        self._table._values[self.name] = v
+
+    @property
+    def is_tunable(self) -> bool:
+        return self.name in self._table._spaces
+
+    @property
+    def is_dynamic(self) -> bool:
+        return self.name in self._table._dynamic
+
+    @property
+    def search_space(self) -> Optional[TunableItemCfg]:
+        return self._table._spaces.get(self.name)
+
+    @search_space.setter
+    def search_space(self, space: TunableItemCfg):
+        self._table._spaces[self.name] = space
+
+
 class PortConfig(object):
-    """One tensor port of a kernel.  A sparse port owns the mask, the block size and the index set
-    built from them; ports of several kernels can be merged with ``connect`` so that one index set
-    serves all of them."""
-    name: str
-    is_input: bool
-    is_sparse: bool = False
-    BCSR: bool = False
-    BCSC: bool = False
+    """One tensor port of a kernel (interface of sparta/specializer/kernels/kernel_base.py:37-80).
 
-    def __post_init__(self):
-        self.mask: Optional[torch.Tensor] = None
-        self._block_H: int = 0
-        self._block_W: int = 0
-        self.indexes: Optional[BCSIndexes] = None
-        self.capacity: Optional[int] = None  # index entries kept per mask (None: every block)
+    A sparse port owns what defines an index set -- the mask tensor, the block shape, which index forms
+    are wanted -- and the ``indexes`` built from them on the GPU.  ``connect`` makes another kernel's port
+    an alias of this one, so several kernels (forward and backward, or the three operators of an
+    attention layer) read one index set; the wanted forms are OR-ed.
+    """
 
-    def set_sparse(self, BCSR: bool, BCSC: bool):
-        self.is_sparse = True
+    def __init__(self, name: str, is_input: bool, is_sparse: bool = False, BCSR: bool = False, BCSC: bool = False):
+        self.name = name
+        self.is_input = is_input
+        self.is_sparse = is_sparse
         self.BCSR = BCSR
         self.BCSC = BCSC
+        self.mask: Optional[torch.Tensor] = None
+        self.indexes: Optional[BCSIndexes] = None
+        self.capacity: Optional[int] = None  # index entries kept per mask (None: every block)
+        self._block = (0, 0)
+
+    def set_sparse(self, BCSR: bool, BCSC: bool):
+        self.is_sparse, self.BCSR, self.BCSC = True, BCSR, BCSC
 
     def set_block_size(self, block_H: int, block_W: int):
-        if self.is_sparse and (block_H != self._block_H or block_W != self._block_W):
-            self._block_H = block_H
-            self._block_W = block_W
-            self._update_indexes()
+        if self.is_sparse and (block_H, block_W) != self._block:
+            self._block = (block_H, block_W)
+            self.refresh()
 
     def set_mask(self, mask: torch.Tensor):
         if self.is_sparse:
             self.mask = mask
-            self._update_indexes()
+            self.refresh()
 
     def refresh(self):
-        """Rebuild the indexes from the current contents of the mask tensor (one kernel launch, no
-        host synchronisation): the per-call conversion used for dynamic sparsity."""
-        self._update_indexes()
-
-    def _update_indexes(self):
-        if self._block_H > 0 and self._block_W > 0 and self.mask is not None:
-            self.indexes = get_bcs_function(
-                self._block_H, self._block_W, self.BCSR, self.BCSC,
-            ).build_indexes(self.mask, self.capacity)
+        """(Re)build the indexes from the current contents of the mask tensor: one kernel launch, no
+        host synchronisation.  Operators in dynamic mode call this at the start of every forward."""
+        block_H, block_W = self._block
+        if self.mask is None or block_H <= 0 or block_W <= 0:
+            return
+        builder = get_bcs_function(block_H, block_W, self.BCSR, self.BCSC)
+        self.indexes = builder.build_indexes(self.mask, self.capacity)
 
     def connect(self, kernel: 'KernelBase', port_name: str):
         other = kernel.ports[port_name]
         assert self.is_sparse == other.is_sparse
-        self.BCSR |= other.BCSR
-        self.BCSC |= other.BCSC
+        self.BCSR = self.BCSR or other.BCSR
+        self.BCSC = self.BCSC or other.BCSC
         kernel.ports[port_name] = self
 
 
 class KernelBase(Callable):
 
     def __init__(self):
-        self._parameters: Dict[str, _Parameter] = {}
+        self._parameters = _ParameterTable()
         self._func: Optional[Callable] = None
         self.ports: Dict[str, PortConfig] = {}
         self.ready = False
@@ -103,30 +153,34 @@ class KernelBase(Callable):
 
     def _add_parameter(self, name: str, value: Any = None, is_tunable: bool = False,
                        is_dynamic: bool = False, search_space: Optional[TunableItemCfg] = None):
-        self._parameters[name] = _Parameter(name, value, is_tunable, is_dynamic, search_space)
+        assert search_space is None or is_tunable
+        if is_tunable and search_space is None:
+            search_space = TunableItemCfg('choice', [] if value is None else [value])
+        self._parameters.add(name, value, search_space, is_dynamic)
 
     def set_search_space(self, search_space: Dict[str, TunableItemCfg]):
         for name, space in search_space.items():
             self._parameters[name].search_space = space
 
     def get_search_space(self, fixed_params: Optional[Dict[str, Any]] = None):
-        """Tunable parameters and their choices; ``None`` when ``fixed_params`` cannot be met."""
-        space = {n: p.search_space for n, p in self._parameters.items() if p.is_tunable}
-        for name, value in (fixed_params or {}).items():
+        """Choices of the tunable parameters, narrowed to ``fixed_params``; ``None`` when this kernel
+        cannot honour them (unknown name, value outside the choices, or a conflicting constant)."""
+        space = {name: row.search_space for name, row in self._parameters.items() if row.is_tunable}
+        for name, wanted in (fixed_params or {}).items():
             if name not in self._parameters:
                 return None
-            param = self._parameters[name]
-            if param.is_tunable:
-                if not param.search_space.includes(value):
+            row = self._parameters[name]
+            if row.is_tunable:
+                if not row.search_space.includes(wanted):
                     return None
-                space[name] = TunableItemCfg('choice', [value])
-            elif param.value is not None and param.value != value:
+                space[name] = TunableItemCfg('choice', [wanted])
+            elif row.value is not None and row.value != wanted:
                 return None
         return space
 
     def set_parameter(self, name: str, value: Any):
-        if name not in self._parameters and name in ['_name', '_impl']:
-            return
+        if name in ('_name', '_impl') and name not in self._parameters:
+            return  # bookkeeping keys of configuration dictionaries
         self._parameters[name].value = value
 
     def set_parameters(self, params: Dict[str, Any]):
@@ -137,9 +191,8 @@ class KernelBase(Callable):
         return self._parameters[name].value
 
     def get_parameters(self, names: Optional[List[str]] = None):
-        if names is None:
-            return {k: v.value for k, v in self._parameters.items()}
-        return {k: self._parameters[k].value for k in names}
+        wanted = self._parameters.keys() if names is None else names
+        return {name: self._parameters[name].value for name in wanted}
 
     @abc.abstractmethod
     def set_shape(self, *args, **kwargs):
