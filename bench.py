@@ -8,9 +8,19 @@ block sparsity (dsd, weight held as BCSR values); metric = TFLOP/s on the FLOPs 
 With N > 1 every rank runs that workload on its own shard of 4096 token rows (weak scaling, no
 collective on the data path).  Rank 0 prints ONE JSON line.
 
-Extras (rank 0, N = 1): the other sparsities and the dds form, the fused sparse attention forward
-(B4 H16 S4096 D64, ms), the GPU mask -> BCSR conversion of 32 masks of 2048 x 2048 (us, GB/s), that
-conversion plus the dds matmul (dynamic sparsity), and the fp32 README workload.
+At every N the line also carries ``ranks`` (minimum / median / maximum over the ranks of the headline step
+and of the end-to-end step, and each rank's host <-> device copy rate) and ``extras.attention_c5_sharded``:
+the large attention configuration (bf16, 64 x 32 heads, S 8192, D 128) with its batch x head dimension
+sharded over the N ranks, forward time per rank, and the optional all-gather of the outputs over NVLink
+(NCCL) timed separately.
+
+Extras (rank 0, N = 1): the other sparsities and the dds form, a dense fp16 GEMM of the same shape beside the
+headline, the fused sparse attention forward (B4 H16 S4096 D64, ms), the GPU mask -> BCSR conversion of 32
+masks of 2048 x 2048 (us, GB/s), that conversion plus the dds matmul (dynamic sparsity), the fp32 README
+workload, and -- when the reference's own kernels have been compiled (``oracle/_ref``) -- those kernels on
+the README and notebook workloads of the reference (``ref_gpu``).  ``--extras refgrid`` (not in the default
+set) runs the grid of the reference's own benchmark scripts: M 3072, K 768, N 4096, mask granularity
+1 / 8 / 32, twelve sparsities.
 
 ``--impl reference`` times the reference's own way of computing the same thing on the host cores:
 masked-dense torch (the computation its unit tests compare against), via the oracle.
@@ -190,6 +200,106 @@ def build_linear(device, sparsity, mode='dsd', tokens=TOKENS, like=None):
     return dict(op=op, fn=fn, x=x, w=w, b=b, mask=mask, xd=xd, nnz=nnz, flops=flops, bytes=bytes_)
 
 
+
+def _sparse_linear_fp(device, x, w, b, mask, tile, dtype):
+    """SparseLinear (weight mask) built for ``tile`` = (BM, BK, BN) on ``dtype`` copies of the inputs."""
+    import sparta_b200 as sparta
+    dense = torch.nn.Linear(w.shape[1], w.shape[0], device=device, dtype=dtype)
+    dense.load_state_dict({'weight': (w * mask).to(device=device, dtype=dtype), 'bias': b.to(device=device, dtype=dtype)})
+    op = sparta.nn.SparseLinear(dense, weight_mask=mask.to(device))
+    xd = x.to(device=device, dtype=dtype)
+    op.build({'forward:C': {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': tile[0], 'BLOCK_SIZE_K_VALUE': tile[1],
+                            'BLOCK_SIZE_N_VALUE': tile[2]}}, sample_inputs=[xd])
+    return op, xd
+
+
+def ref_gpu_extras(device, timed):
+    """The reference's dsd kernels (32 x 32 x 32 ``sparta`` tile with 4 x 4 x 4 thread tiles, and the fixed
+    32 x 64 x 32 ``openai`` kernel; fp32, the only type they have) on two workloads of the reference itself:
+    the README example (1024^3, 8 x 8-block mask, 90 %) and the notebook examples/sparse_linear.ipynb
+    (4096 x 3072 -> 768, 32 x 32 blocks, 80 %).  ``kernel_us`` times the kernel alone on a pre-zeroed
+    output; ``call_us`` adds the torch.zeros the reference allocates per call
+    (sparta/specializer/kernels/matmul.py:171).  This library runs beside it in fp32 (FMA kernel) and fp16
+    (tcgen05 kernel) through the public operator."""
+    from oracle import oracle, ref_kernels
+    ref = ref_kernels.ReferenceKernels()
+    out = {}
+    for name, (M, K, N, gran, sp) in {'readme_1024_8x8_90': (1024, 1024, 1024, 8, 0.9),
+                                      'notebook_4096x3072x768_32x32_80': (4096, 3072, 768, 32, 0.8)}.items():
+        g = torch.Generator().manual_seed(2022)
+        x = torch.rand((M, K), generator=g)
+        w = torch.rand((N, K), generator=g)
+        b = torch.rand((N,), generator=g)
+        mask = oracle.block_mask((N, K), (gran, gran), sp, generator=g)
+        xd, wd, bd, md = x.to(device), (w * mask).to(device), b.to(device), mask.to(device)
+        want = torch.nn.functional.linear(xd, wd, bd)
+        rec = {}
+        for impl, tile in (('sparta', (32, 32, 32)), ('openai', (32, 64, 32))):
+            ix = ref.build_indexes(md, tile[2], tile[1], True, False)  # dsd, B stored [N, K]: BN x BK blocks, BCSR
+            wc = ref.convert(wd.unsqueeze(0), ix)
+            c = torch.zeros((1, M, N), device=device)
+            got = ref.matmul(impl, 'dsd', xd.unsqueeze(0), wc, bd.unsqueeze(0), ix, M, K, N, False, True, True)
+            err = float((got[0] - want).abs().max())
+            kernel_ms = timed(lambda: ref.matmul(impl, 'dsd', xd.unsqueeze(0), wc, bd.unsqueeze(0), ix, M, K, N,
+                                                 False, True, True, out=c), steps=10)
+            call_ms = timed(lambda: ref.matmul(impl, 'dsd', xd.unsqueeze(0), wc, bd.unsqueeze(0), ix, M, K, N,
+                                               False, True, True), steps=10)
+            rec[f'reference_{impl}_fp32'] = {'kernel_us': round(kernel_ms * 1e3, 2), 'call_us': round(call_ms * 1e3, 2),
+                                             'covering_blocks': ix['nnz'], 'max_abs_err_vs_dense': err}
+        small = gran < 32
+        op, xs = _sparse_linear_fp(device, x, w, b, mask, (64, gran, gran) if small else (64, 32, 32), torch.float32)
+        rec['this_library_fp32'] = {'call_us': round(timed(lambda: op(xs), steps=10) * 1e3, 2),
+                                    'max_abs_err_vs_dense': float((op(xs) - want).abs().max())}
+        if not small:
+            op16, x16 = _sparse_linear_fp(device, x, w, b, mask, (token_tile(), 32, 32), torch.float16)
+            rec['this_library_fp16'] = {'call_us': round(timed(lambda: op16(x16), steps=10) * 1e3, 2)}
+        rec['dense_torch_fp32_us'] = round(timed(lambda: torch.nn.functional.linear(xd, wd, bd), steps=10) * 1e3, 2)
+        out[name] = rec
+    return out
+
+
+def refgrid_extras(device, timed):
+    """Forward latency over the grid of the reference's benchmark scripts
+    (test/bench/matmul/matmul.py:18-23: M 3072, K 768, N 4096, mask granularity 1 / 8 / 32, twelve
+    sparsities; B sparse, stored [N, K], compressed), in microseconds: torch dense fp32 and fp16, this
+    library fp32 (FMA kernel, 32 x 32 blocks over the finer mask like the reference's tuned configurations)
+    and fp16 (tcgen05), and the reference's 32 x 64 x 32 kernel when compiled."""
+    from oracle import oracle, ref_kernels
+    M, K, N = 3072, 768, 4096
+    ref = ref_kernels.ReferenceKernels() if ref_kernels.available() else None
+    rows = []
+    for gran in (1, 8, 32):
+        for sp in (0, 0.2, 0.4, 0.6, 0.8, 0.9, 0.95, 0.99, 0.995, 0.999, 0.9995, 0.9999):
+            g = torch.Generator().manual_seed(2022)
+            x = torch.rand((M, K), generator=g)
+            w = torch.rand((N, K), generator=g)
+            b = torch.zeros((N,))
+            mask = oracle.block_mask((N, K), (gran, gran), sp, generator=g)
+            if int(mask.sum()) == 0:
+                continue
+            xd, wd = x.to(device), (w * mask).to(device)
+            row = {'granularity': gran, 'sparsity': sp,
+                   'dense_fp32_us': round(timed(lambda: torch.matmul(xd, wd.T), steps=5) * 1e3, 1)}
+            xh, wh = xd.half(), wd.half()
+            row['dense_fp16_us'] = round(timed(lambda: torch.matmul(xh, wh.T), steps=5) * 1e3, 1)
+            op, xs = _sparse_linear_fp(device, x, w, b, mask, (64, 32, 32), torch.float32)
+            row['ours_fp32_us'] = round(timed(lambda: op(xs), steps=5) * 1e3, 1)
+            row['covering_blocks_32x32'] = op.get_sparse_indexes('B').block_nnz
+            op16, x16 = _sparse_linear_fp(device, x, w, b, mask, (token_tile(), 32, 32), torch.float16)
+            row['ours_fp16_us'] = round(timed(lambda: op16(x16), steps=5) * 1e3, 1)
+            if ref is not None:
+                md = mask.to(device)
+                ix = ref.build_indexes(md, 32, 64, True, False)
+                wc = ref.convert(wd.unsqueeze(0), ix)
+                c = torch.zeros((1, M, N), device=device)
+                row['reference_openai_fp32_us'] = round(timed(
+                    lambda: ref.matmul('openai', 'dsd', xd.unsqueeze(0), wc, None, ix, M, K, N, False, True, True, out=c),
+                    steps=5) * 1e3, 1)
+            rows.append(row)
+            del op, op16
+    return rows
+
+
 def run_extras(device, peaks, flush, only=None):
     """Secondary measurements (each: 3 warm-ups, 10 timed steps, L2 flushed between steps)."""
     import sparta_b200 as sparta
@@ -264,32 +374,6 @@ def run_extras(device, peaks, flush, only=None):
     except Exception as e:
         extras['softmax_b4h16s4096_compressed'] = {'error': repr(e)[:200]}
 
-    # the large attention configuration: bf16, 64 x 32 = 2048 heads, S 8192, D 128 (17 GB of q, k, v, o),
-    # same mask generator on a 128 x 128 grid of 64 x 64 blocks; one GPU holds all heads here, the
-    # multi-GPU form shards the head dimension with no exchange
-    try:
-        if not want('attention_large'):
-            raise KeyError('skipped')
-        heads, S, D = 2048, 8192, 128
-        dg = torch.Generator(device=device).manual_seed(2025)
-        q, k, v = (torch.randn((heads, S, D), generator=dg, device=device, dtype=torch.bfloat16) for _ in range(3))
-        amask = oracle.band_global_random_mask(S, S, 64, 8, 0.05, seed=0).to(device)
-        attn = sparta.nn.SparseAttention(mask=amask)
-        mm = {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': 64, 'BLOCK_SIZE_K_VALUE': 64, 'BLOCK_SIZE_N_VALUE': 64}
-        sm = {'_impl': 'sparta', 'BLOCK_SIZE_H_VALUE': 64, 'BLOCK_SIZE_W_VALUE': 64, 'ROW_TILE_VALUE': 4}
-        attn.build({'qk/forward:C': mm, 'sm/forward:y': sm, 'out/forward:C': mm}, sample_inputs=[q, k, v])
-        nnz = attn.get_sparse_indexes().block_nnz
-        ms = time_steps(lambda: attn(q, k, v), 3, 3, lambda: None) / 3  # inputs (17 GB) are far larger than L2
-        flops = 4.0 * heads * nnz * 64 * 64 * D
-        extras['attention_b64h32s8192d128_bf16'] = {
-            'fwd_ms': round(ms, 3), 'nnz_blocks': nnz, 'fused': bool(attn._use_fused),
-            'tflops': round(flops / ms / 1e9, 2), 'frac_tensor_peak': round(flops / ms / 1e9 / peaks['tflops'], 4),
-            'gbs': round(4.0 * heads * S * D * 2 / ms / 1e6, 1)}
-        del q, k, v, attn
-        torch.cuda.empty_cache()
-    except Exception as e:
-        extras['attention_b64h32s8192d128_bf16'] = {'error': repr(e)[:200]}
-
     # mask -> BCSR on the GPU: 32 masks of 2048 x 2048, 32x32 blocks, 90 % sparse
     try:
         if not want('convert'):
@@ -361,7 +445,115 @@ def run_extras(device, peaks, flush, only=None):
                                              'gflops': round(2.0 * 1024 * 64 * nnz / ms / 1e6, 1)}
     except Exception as e:
         extras['linear_fp32_1024_8x8_90'] = {'error': repr(e)[:200]}
+
+    # a dense fp16 GEMM of the headline's shape through torch (cuBLAS), same events and flush: the
+    # comparison the reference's own benchmark makes (test/bench/matmul/matmul.py:143-156,192)
+    try:
+        if not want('dense'):
+            raise KeyError('skipped')
+        x, w, b, mask = linear_inputs(SPARSITY)
+        xd, wd, bd = x.to(device), w.to(device), b.to(device)
+        ms = timed(lambda: torch.nn.functional.linear(xd, wd, bd), steps=20)
+        kept = int((mask.reshape(OUT_F // BLOCK, BLOCK, IN_F // BLOCK, BLOCK).amax((1, 3)) > 0).sum())
+        extras['dense_fp16_4096'] = {
+            'ms': round(ms, 4), 'dense_tflops': round(2.0 * TOKENS * IN_F * OUT_F / ms / 1e9, 1),
+            'nnz_block_tflops_equiv_75': round(2.0 * TOKENS * BLOCK * BLOCK * kept / ms / 1e9, 1),
+            'note': 'torch.nn.functional.linear on the masked-dense fp16 weight (zeros multiplied), library GEMM'}
+        del xd, wd, bd
+    except Exception as e:
+        extras['dense_fp16_4096'] = {'error': repr(e)[:200]}
+
+    # the reference's own kernels (rendered from its templates, compiled for sm_100a) beside this library
+    try:
+        if not want('ref_gpu'):
+            raise KeyError('skipped')
+        from oracle import ref_kernels
+        if not ref_kernels.available():
+            raise RuntimeError('oracle/_ref not built (no checkout of the reference at build time)')
+        extras['ref_gpu'] = ref_gpu_extras(device, timed)
+    except Exception as e:
+        extras['ref_gpu'] = {'error': repr(e)[:200]}
+
+    try:
+        if only is None or 'refgrid' not in only:
+            raise KeyError('skipped')
+        extras['refgrid'] = refgrid_extras(device, timed)
+    except Exception as e:
+        extras['refgrid'] = {'error': repr(e)[:200]}
     return {k: v for k, v in extras.items() if 'skipped' not in str(v.get('error', ''))}
+
+
+
+def rank_summary(local, world, device):
+    """min / median / max over the ranks of each value of ``local`` (a dict of floats); every rank calls."""
+    names = sorted(local)
+    mine = torch.tensor([float(local[n]) for n in names], dtype=torch.float64, device=device)
+    if world > 1:
+        import torch.distributed as dist
+        rows = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(rows, mine)
+        table = torch.stack(rows)
+    else:
+        table = mine.unsqueeze(0)
+    out = {}
+    for i, n in enumerate(names):
+        col = table[:, i].sort().values
+        out[n] = {'min': round(float(col[0]), 5), 'median': round(float(col[len(col) // 2]), 5),
+                  'max': round(float(col[-1]), 5)}
+    return out
+
+
+def attention_c5_sharded(device, world, rank, peaks, barrier):
+    """The large attention configuration -- bf16, 64 x 32 = 2048 heads, S 8192, D 128, the band + global +
+    random mask on a 128 x 128 grid of 64 x 64 blocks -- with the batch x head dimension sharded over the
+    ranks (``parallel.shard_bounds``); masks and indexes are replicated, there is no exchange on the data
+    path.  The optional all-gather of the outputs (NCCL, every rank ends up with all 2048 heads) is timed on
+    its own.  Every rank calls; returns the same dictionary on every rank."""
+    import sparta_b200 as sparta
+    from sparta_b200 import parallel
+    from oracle import oracle  # mask generator shared with the checker
+    heads_total, S, D = 2048, 8192, 128
+    lo, hi = parallel.shard_bounds(heads_total, world, rank)
+    heads = hi - lo
+    dg = torch.Generator(device=device).manual_seed(2025 + rank)
+    q, k, v = (torch.randn((heads, S, D), generator=dg, device=device, dtype=torch.bfloat16) for _ in range(3))
+    amask = oracle.band_global_random_mask(S, S, 64, 8, 0.05, seed=0).to(device)
+    attn = sparta.nn.SparseAttention(mask=amask)
+    mm = {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': 64, 'BLOCK_SIZE_K_VALUE': 64, 'BLOCK_SIZE_N_VALUE': 64}
+    sm = {'_impl': 'sparta', 'BLOCK_SIZE_H_VALUE': 64, 'BLOCK_SIZE_W_VALUE': 64, 'ROW_TILE_VALUE': 4}
+    attn.build({'qk/forward:C': mm, 'sm/forward:y': sm, 'out/forward:C': mm}, sample_inputs=[q, k, v])
+    nnz = attn.get_sparse_indexes().block_nnz
+    no_flush = lambda: None  # the operands of a rank (17 GB / world) are far larger than L2
+    with torch.no_grad():
+        fwd_ms = time_steps(lambda: attn(q, k, v), 3, 3, no_flush, barrier) / 3
+        o = attn(q, k, v)
+    local = {'fwd_ms': fwd_ms}
+    gather = {}
+    if world > 1:
+        import torch.distributed as dist
+        full = torch.empty((heads_total, S, D), dtype=o.dtype, device=device)
+        ag_ms = time_steps(lambda: parallel.all_gather_outputs(o, out=full), 3, 2, no_flush, barrier) / 3
+        local['allgather_ms'] = ag_ms
+        received = (heads_total - heads) * S * D * 2
+        local['allgather_in_gbs'] = received / ag_ms / 1e6
+        ok = bool(torch.equal(full[lo:hi], o))
+        flag = torch.tensor([1 if ok else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        gather = {'allgather_bytes_received_per_rank': received, 'allgather_own_shard_intact': bool(flag.item()),
+                  'collective': 'NCCL all_gather_into_tensor over NVLink / NVSwitch'}
+        del full
+    stats = rank_summary(local, world, device)
+    flops = 4.0 * heads_total * nnz * 64 * 64 * D
+    worst = stats['fwd_ms']['max']
+    out = {'heads_per_rank': heads, 'nnz_blocks': nnz, 'fused': bool(attn._use_fused), 'dtype': 'bf16',
+           'fwd_ms': stats['fwd_ms'], 'aggregate_tflops': round(flops / worst / 1e9, 1),
+           'frac_tensor_peak_per_gpu': round(flops / world / worst / 1e9 / peaks['tflops'], 4), **gather}
+    for name in ('allgather_ms', 'allgather_in_gbs'):
+        if name in stats:
+            out[name] = stats[name]
+    del q, k, v, o, attn
+    torch.cuda.empty_cache()
+    return out
 
 
 def cpu_baseline_linear(x, w, b, repeats=3):
@@ -395,7 +587,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-extras', action='store_true')
     ap.add_argument('--extras', default=None,
-                    help='comma list of extra measurements to run: linear,attention,softmax,attention_large,convert,readme (default all)')
+                    help='comma list of extra measurements to run: linear,dense,attention,attention_c5,softmax,convert,readme,ref_gpu (default: all of these), refgrid (only when named)')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
 
@@ -468,6 +660,10 @@ def main():
     e2e_ms = time_steps(e2e_step, args.steps, args.warmup, flush, barrier)
     clocks = sampler.stop() if rank == 0 else None
 
+    # per-rank view first (who is slow?), then the maximum over the ranks, which is what the line reports
+    h2d_bytes, d2h_bytes = x_host.numel() * 2, y_host.numel() * 2
+    ranks = rank_summary({'step_ms': total_ms / args.steps, 'e2e_ms': e2e_ms / args.steps,
+                          'e2e_host_link_gbs': (h2d_bytes + d2h_bytes) / (e2e_ms / args.steps) / 1e6}, world, device)
     times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=device)
     if world > 1:
         import torch.distributed as dist
@@ -476,6 +672,26 @@ def main():
     ms_per_step = total_ms / args.steps
     value = world * wl['flops'] / ms_per_step / 1e9
     e2e_value = world * wl['flops'] / (e2e_ms / args.steps) / 1e9
+
+    # full-size parity of the headline against the oracle (masked-dense fp32 on the host), outside any timed region
+    parity = None
+    if rank == 0:
+        want = torch.nn.functional.linear(wl['x'][:512].float(), wl['w'].float(), wl['b'].float())
+        got = wl['fn']()[:512].float().cpu()
+        parity = {'max_abs_err': float((got - want).abs().max()), 'tolerance': 2e-2,
+                  'checked': 'first 512 token rows of the device-resident headline output against F.linear in fp32 on the host; '
+                             'the end-to-end output was checked against the device-resident one'}
+        if not torch.allclose(got, want, rtol=2e-2, atol=2e-2):
+            raise RuntimeError(f'headline result differs from the oracle: {parity}')
+
+    # the sharded attention configuration runs on every rank, at every N (not for --no-extras)
+    c5 = None
+    if not args.no_extras and (args.extras is None or 'attention_c5' in args.extras.split(',')):
+        del chunk, streamed
+        try:
+            c5 = attention_c5_sharded(device, world, rank, peaks, barrier)
+        except Exception as e:  # an extra must not take the headline number down
+            c5 = {'error': repr(e)[:200]}
 
     if rank == 0:
         kernel_tflops = wl['flops'] / ms_per_step / 1e9
@@ -490,11 +706,13 @@ def main():
                          'peak_source': f"{peaks['source']} bf16 burst", 'hbm_gbs': wl['bytes'] / ms_per_step / 1e6,
                          'hbm_frac': wl['bytes'] / ms_per_step / 1e6 / peaks['hbm_gbs']},
             'e2e': {'value': e2e_value, 'unit': 'TFLOP/s', 'ms_per_step': e2e_ms / args.steps,
-                    'h2d_bytes_per_step': x_host.numel() * 2, 'd2h_bytes_per_step': y_host.numel() * 2,
+                    'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': d2h_bytes,
                     'how': f'SparseLinear built for {E2E_CHUNK} rows, called through sparta.nn.HostStreamedRows: '
                            f'{TOKENS // E2E_CHUNK} chunks, copy-in / kernel / copy-out overlapped on three streams'},
             'gpu_launches': args.steps,
             'clocks': clocks,
+            'ranks': ranks,
+            'parity': parity,
         }
         if world == 1:
             secs, cores = cpu_baseline_linear(wl['x'], wl['w'], wl['b'])
@@ -503,6 +721,8 @@ def main():
             if not args.no_extras:
                 only = set(args.extras.split(',')) if args.extras else None
                 out['extras'] = run_extras(device, peaks, flush, only)
+        if c5 is not None:
+            out.setdefault('extras', {})['attention_c5_sharded'] = c5
         print(json.dumps(out))
     if world > 1:
         import torch.distributed as dist

@@ -158,7 +158,7 @@ int sparta_bcs_sum(const void* vals, void* out, const int32_t* row_ptr, const in
  *                   (pass idx_capacity or the host's nnz if known; <= 0 lets the library choose).
  * SPARTA_IMPL_TCGEN05 covers, for fp16 / bf16 (fp32 accumulation):
  *   dsd  trans_a = 0, trans_b = 1, compressed = 1, 32-bit BCSR, BM = 128, BK = BN = 32, M % 128 == 0,
- *        K <= 16384, one index set (the SparseLinear weight layout);
+ *        K <= 8192, one index set (the SparseLinear weight layout);
  *   dds  trans_a = 0, 32-bit BCSR, BM = BN = 32, BK = 64, M % 128 == 0, N <= 32768, compressed or
  *        dense output, one index set or one per batch element;
  * and returns SPARTA_ERR_UNSUPPORTED otherwise.  SPARTA_IMPL_SIMT (and AUTO outside that coverage)

@@ -9,8 +9,14 @@
 // the two rows into a sorted list of K blocks with two presence bits each; K blocks are then taken
 // two at a time, so that both contractions run as full-width instructions:
 //   S[128, 128] = Q[128, D] . [K_a; K_b]^T           (tcgen05.mma M128 N128, D/16 of them)
-//   P = exp2(S * scale * log2e - m)  in registers, masked per row half and per element, -> smem
-//   O[128, D] += P[128, 128] . [V_a; V_b]             (tcgen05.mma M128 N=D, B operand MN-major)
+//   P = exp2(S * scale * log2e - m)  in registers, masked per row half and per element, -> tensor memory
+//   O[128, D] += P[128, 128] . [V_a; V_b]             (tcgen05.mma M128 N=D, A = P from tensor memory,
+//                                                      B operand MN-major in shared memory)
+// The scores of a step are read from tensor memory once and stay in registers between the row-maximum pass
+// and the exponential pass, so the score buffer is released right after the read; P goes back to tensor
+// memory with one tcgen05.st per thread (no shared-memory round trip, no proxy fence), which also takes
+// the 4 KB A-operand read of every P.V instruction off the shared-memory port (with D = 64 that read made
+// the instruction take 48 cycles for 32 cycles of math).
 // Warps: 0-7 softmax (two threads per row, one for each K block of the pair; online max / sum with a
 // lazy rescale of O: the running max is only raised when it grows by more than 8 in log2 units), 8 TMA
 // producer, 9 issues the Q.K^T MMAs, 10 issues the P.V MMAs.  All mbarrier waits are bounded (status words of sparta_last_status).
@@ -56,16 +62,19 @@ struct AttnParams {
 template <int D>
 struct Cfg {
   static constexpr int kSBuf = D == 64 ? 1 : 2;      // score buffers in tensor memory
-  static constexpr int kKStages = D == 64 ? 1 : 2;
+  static constexpr int kKStages = 2;
   static constexpr int kVStages = 2;
   static constexpr int kChunks = D / 64;             // 64-element (128-byte) chunks of the head dim
   static constexpr int kQBytes = kTileM * D * 2;
   static constexpr int kKVBytes = kPair * D * 2;     // one stage: two blocks
-  static constexpr int kPBytes = kTileM * kPair * 2;
+  // tensor memory columns: scores (128 per buffer), the output accumulator (D), the probabilities as 16-bit
+  // pairs (64): 256 columns for D = 64 (two CTAs share an SM), 512 for D = 128
   static constexpr uint32_t kTmemCols = D == 64 ? 256 : 512;
   static constexpr uint32_t kOCol = kSBuf * kPair;
+  static constexpr uint32_t kPCol = kOCol + D;
+  static_assert(kPCol + kPair / 2 <= kTmemCols, "tensor memory budget");
   static constexpr int kListBytes = kMaxKb * 2 + kMaxKb;  // ulist (uint16) + kmask (uint8)
-  static constexpr int kSmem = kQBytes + (kKStages + kVStages) * kKVBytes + kPBytes + kListBytes + 512 + 1024;
+  static constexpr int kSmem = kQBytes + (kKStages + kVStages) * kKVBytes + kListBytes + 512 + 1024;
 };
 
 template <int D, int FMT>
@@ -81,8 +90,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint8_t* q_s = smem;
   uint8_t* k_s = q_s + C::kQBytes;
   uint8_t* v_s = k_s + kKStages * C::kKVBytes;
-  uint8_t* p_s = v_s + kVStages * C::kKVBytes;
-  uint16_t* ulist = reinterpret_cast<uint16_t*>(p_s + C::kPBytes);  // (K block << 2) | presence bits
+  uint16_t* ulist = reinterpret_cast<uint16_t*>(v_s + kVStages * C::kKVBytes);  // (K block << 2) | presence bits
   uint8_t* kmask = reinterpret_cast<uint8_t*>(ulist + kMaxKb);
   uint8_t* ctl = kmask + kMaxKb;
   uint64_t* q_full = reinterpret_cast<uint64_t*>(ctl);
@@ -212,11 +220,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (!ok && lane == 0) atomicExch(&p.status[1], 1);
   } else if (warp == kWarpPV) {
     // ------------------------------ O += P V ------------------------------
-    // P: K-major, two 64-key chunks of [128 rows x 128 B]; V: MN-major (head dim contiguous), 8 keys
-    // per 1024-byte group, 64-element chunks of the head dim kPair * 128 bytes apart.
-    const uint64_t p_desc_hi = make_smem_desc(0, 16, 1024, SW_128B);
+    // P: A operand in tensor memory, lane = row, two 16-bit probabilities per column, keys in order (eight
+    // columns per K = 16 slab); V: MN-major (head dim contiguous), 8 keys per 1024-byte group, 64-element
+    // chunks of the head dim kPair * 128 bytes apart.
     const uint64_t v_desc_hi = make_smem_desc(0, kPair * 128, 1024, SW_128B);
-    const uint32_t p_lo = smem_u32(p_s) >> 4, v_lo = smem_u32(v_s) >> 4;
+    const uint32_t v_lo = smem_u32(v_s) >> 4;
     constexpr uint32_t idesc = make_idesc_f16(kTileM, D, FMT, 0, 1);
     bool ok = true;
     for (int j = 0; j < npairs && ok; ++j) {
@@ -227,9 +235,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tc_fence_after_sync();
       if (lane == 0) {
         for (int kk = 0; kk < nblk * (kBlk / 16); ++kk) {
-          const uint32_t a_off = ((kk / 4) * (kTileM * 128) + (kk % 4) * 32) >> 4;
           const uint32_t b_off = (vs * C::kKVBytes + kk * 16 * 128) >> 4;
-          umma_ss(tmem_base + C::kOCol, p_desc_hi | (p_lo + a_off), v_desc_hi | (v_lo + b_off), idesc,
+          umma_ts(tmem_base + C::kOCol, tmem_base + C::kPCol + kk * 8, v_desc_hi | (v_lo + b_off), idesc,
                   (j > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&v_empty[vs]);
@@ -263,32 +270,59 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const bool mine = (e >> half) & 1;       // this thread's block is kept in its block row (warp-uniform)
       const int kb = e >> 2;
       const uint32_t s_addr = tmem_base + lane_base + sb * kPair + colhalf * kBlk;
-      // ---- pass 1: row maximum over the kept, unmasked scores of this thread's block ----
+      // ---- the 64 scores of this thread's block: masked elements set to -inf, row maximum.  With D = 128
+      // (one CTA per SM, registers to spare) they are read once and stay in registers, and the score buffer
+      // is released here; with D = 64 (two CTAs per SM, 80 registers) they are read again for the second pass
+      constexpr bool kHold = D == 128;
+      uint32_t r[kHold ? 64 : 32];
       float mx = -INFINITY;
+      auto mask_scores = [&](uint32_t* v, int h) {  // 32 scores starting at key 32 h of the block
+        const uint4* mrow = reinterpret_cast<const uint4*>(p.mask + grow * p.Ns + (long long)kb * kBlk + h * 32);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint4 m4 = __ldg(mrow + q);
+          const uint32_t mw[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (!((mw[i >> 2] >> (8 * (i & 3))) & 0xffu)) v[16 * q + i] = 0xff800000u;  // -inf
+        }
+      };
       if (ok) {
         if (!mbar_wait_warp(&s_full[sb], (j / kSBuf) & 1)) {
           ok = false;
         } else {
           tc_fence_after_sync();
           if (mine) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              uint32_t r[32];
-              tmem_ld_x32(s_addr + h * 32, r);
+            if constexpr (kHold) {
+              tmem_ld_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+              tmem_ld_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
               tmem_ld_wait();
-              if (p.mask) {
-                const uint8_t* mrow = p.mask + grow * p.Ns + (long long)kb * kBlk + h * 32;
-                const uint4 m0 = __ldg(reinterpret_cast<const uint4*>(mrow));
-                const uint4 m1 = __ldg(reinterpret_cast<const uint4*>(mrow) + 1);
-                const uint32_t mw[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+              if (p.mask) { mask_scores(&r[0], 0); mask_scores(&r[32], 1); }
+              {  // four independent chains: one chain of 64 dependent maxima would cost ~300 cycles of latency
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  if ((mw[i >> 2] >> (8 * (i & 3))) & 0xffu) mx = fmaxf(mx, __uint_as_float(r[i]));
-              } else {
+                for (int i = 0; i < 64; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[i]));
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+              }
+            } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+              for (int h = 0; h < 2; ++h) {
+                tmem_ld_x32(s_addr + h * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                tmem_ld_wait();
+                if (p.mask) mask_scores(&r[0], h);
+                {
+                  float m4[4] = {mx, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[i]));
+                  mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                }
               }
             }
+          }
+          if constexpr (kHold) {  // the scores are in registers: the buffer may take the next S
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[sb]);
           }
         }
       }
@@ -310,75 +344,70 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tc_fence_after_sync();
 #pragma unroll
         for (int c = colhalf * kOChunks; c < (colhalf + 1) * kOChunks; ++c) {
-          uint32_t r[32];
-          tmem_ld_x32(tmem_base + lane_base + C::kOCol + c * 32, r);
+          uint32_t o[32];
+          tmem_ld_x32(tmem_base + lane_base + C::kOCol + c * 32, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st_x32(tmem_base + lane_base + C::kOCol + c * 32, r);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_x32(tmem_base + lane_base + C::kOCol + c * 32, o);
         }
-        tmem_st_wait();
       }
-      // ---- pass 2: P = exp2(S * scale * log2e - m) -> shared memory (K-major, 128-byte swizzle) ----
-      if (colhalf < nblk) {  // this thread's block of the pair
-        uint8_t* prow = p_s + colhalf * (kTileM * 128) + row * 128;
+      // ---- P = exp2(S * scale * log2e - m) as 16-bit pairs -> tensor memory (this thread's 32 columns) ----
+      if (colhalf < nblk) {  // this thread's block of the pair (warp-uniform)
+        // every score of this row masked so far: subtracting +inf makes every probability zero
+        const float neg_m = m_run > -INFINITY ? -m_run : -INFINITY;
+        float sum = 0.f, sum1 = 0.f;
+        auto exp_pack = [&](const uint32_t* v, uint32_t* out) {  // 32 scores -> 16 packed pairs (out may be v)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t packed[16];
-          if (mine) {  // warp-uniform: tcgen05.ld needs the whole warp
-            uint32_t r[32];
-            tmem_ld_x32(s_addr + h * 32, r);
-            tmem_ld_wait();
-            // every score of this row masked so far: subtracting +inf makes every probability zero
-            const float neg_m = m_run > -INFINITY ? -m_run : -INFINITY;
-            uint32_t mw[8];
-            if (p.mask) {
-              const uint8_t* mrow = p.mask + grow * p.Ns + (long long)kb * kBlk + h * 32;
-              const uint4 m0 = __ldg(reinterpret_cast<const uint4*>(mrow));
-              const uint4 m1 = __ldg(reinterpret_cast<const uint4*>(mrow) + 1);
-              mw[0] = m0.x; mw[1] = m0.y; mw[2] = m0.z; mw[3] = m0.w;
-              mw[4] = m1.x; mw[5] = m1.y; mw[6] = m1.z; mw[7] = m1.w;
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, neg_m));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, neg_m));
+            // the row sum takes the fp32 probabilities: their rounding to 16 bits for P V is unbiased, and
+            // converting them back cost two instructions per pair in warps bound by instruction issue
+            // (two alternating partial sums keep the additions from forming one dependent chain)
+            if (i & 1) sum1 += p0 + p1; else sum += p0 + p1;
+            if constexpr (FMT == 0) {
+              const __half2 hv = __floats2half2_rn(p0, p1);
+              out[i] = *reinterpret_cast<const uint32_t*>(&hv);
+            } else {
+              const __nv_bfloat162 hv = __floats2bfloat162_rn(p0, p1);
+              out[i] = *reinterpret_cast<const uint32_t*>(&hv);
             }
-            float sum = 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, neg_m));
-              float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, neg_m));
-              if (p.mask) {
-                if (!((mw[(2 * i) >> 2] >> (8 * ((2 * i) & 3))) & 0xffu)) p0 = 0.f;
-                if (!((mw[(2 * i + 1) >> 2] >> (8 * ((2 * i + 1) & 3))) & 0xffu)) p1 = 0.f;
-              }
-              // the row sum takes the fp32 probabilities: their rounding to 16 bits for P V is unbiased, and
-              // converting them back cost two instructions per pair in warps bound by instruction issue
-              sum += p0 + p1;
-              if constexpr (FMT == 0) {
-                const __half2 hv = __floats2half2_rn(p0, p1);
-                packed[i] = *reinterpret_cast<const uint32_t*>(&hv);
-              } else {
-                const __nv_bfloat162 hv = __floats2bfloat162_rn(p0, p1);
-                packed[i] = *reinterpret_cast<const uint32_t*>(&hv);
-              }
-            }
-            l_run += sum;
+          }
+        };
+        const uint32_t p_addr = tmem_base + lane_base + C::kPCol + colhalf * (kBlk / 2);
+        if constexpr (kHold) {
+          if (mine) {
+            exp_pack(&r[0], &r[0]);
+            exp_pack(&r[32], &r[16]);
           } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) packed[i] = 0;
+            for (int i = 0; i < 32; ++i) r[i] = 0;
           }
-          // 32 keys = 64 bytes = four 16-byte chunks; chunk index XOR (row % 8) is the 128-byte swizzle
+          tmem_st_x32(p_addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        } else {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int chunk = (h * 4 + q) ^ (row & 7);
-            *reinterpret_cast<uint4*>(prow + chunk * 16) =
-                make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+          for (int h = 0; h < 2; ++h) {
+            uint32_t packed[16];
+            if (mine) {
+              tmem_ld_x32(s_addr + h * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+              tmem_ld_wait();
+              if (p.mask) mask_scores(&r[0], h);
+              exp_pack(&r[0], packed);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) packed[i] = 0;
+            }
+            tmem_st_x16(p_addr + h * 16, packed);
           }
         }
+        l_run += sum + sum1;
       }
-      // S may be overwritten, P may be read by the tensor core
+      tmem_st_wait();  // P and a rescaled O are in tensor memory
       tc_fence_before_sync();
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&s_empty[sb]);
+        if constexpr (!kHold) mbar_arrive(&s_empty[sb]);  // S may be overwritten
         mbar_arrive(p_full);
       }
     }

@@ -24,8 +24,8 @@
 // 75 % sparsity, 5 % at 95 %; 10 % slower at 50 %), although only two to four of the larger activation
 // tiles fit in tensor memory.  A step is in flight for 3-4 thousand cycles (load issue, load latency,
 // conversion, MMA issue, four hand-offs) while its MMAs take a few hundred, so each resource is held
-// only as long as it is needed: an X tile's shared-memory slot (kXSlots = 3) until the converters
-// have read it, a W block's ring slot (kWSlots = 48 blocks) and the activation slot until the step's
+// only as long as it is needed: an X tile's shared-memory slot (four, or three beside 48 W slots) until the
+// converters have read it, a W block's ring slot (40 or 48 blocks) and the activation slot until the step's
 // MMAs are done; the "full" barriers form a ring of kSSlots = 12 steps.  The prologue turns the BCSR
 // rows of the panel into a complete schedule in shared memory -- per step its K-group, the W blocks
 // it needs (kmask of its K-blocks), where each of them sits in the value array (wsrc), its position
@@ -77,9 +77,16 @@ constexpr int kXBytes = kSubTiles * kSubBytes;
 constexpr int kWBytes = kBlk * kBlk * 2;      // 2 KB
 constexpr int kACols = kStepK / 2;  // tensor-memory columns of one activation tile (two 16-bit values per column)
 constexpr int kNPMax = 12;          // block columns per CTA: 8, 10 or 12, chosen per launch (template parameter NP)
-constexpr int kMaxKb = kG == 2 ? 1024 : 512;  // K-blocks the schedule can hold (K <= 32768 or 16384): shared-memory budget
+constexpr int kMaxKb = kG == 2 ? 512 : 256;   // K-blocks the schedule can hold (K <= 16384 or 8192): shared-memory budget
 constexpr int kMaxSteps = kMaxKb / kG;
-constexpr int kXSlots = kG == 2 ? 5 : 3;  // X tiles in shared memory (80 / 96 KB); a slot is free again once its tile is in tensor memory
+// X tiles in shared memory; a slot is free again once its tile is in tensor memory.  A load takes well over a
+// thousand cycles from issue to landing, a step should take a few hundred, and a slot is tied up for the whole
+// flight: the number of X slots bounds the step rate (three slots: a step per ~630 cycles at best).  Panels of up
+// to ten block columns need only 40 W slots, which leaves room for a fourth X slot (DEEP_X).  Measured on 4096^3:
+// the fourth X slot wins 3 % at 90 / 95 % sparsity, where a step holds few W blocks, and loses 8 % at 75 %, where
+// the W ring is the scarcer resource; the launcher picks by the density of the mask.
+constexpr int x_slots(int np, bool deep_x) { return kG == 2 ? 5 : ((np >= 12 || !deep_x) ? 3 : 4); }
+constexpr int kXSlotsMax = kG == 2 ? 5 : 4;
 constexpr int kSSlots = 12;         // steps in flight between the first load and the last MMA: size of the "full" barrier ring
 constexpr int kPair = kG == 2 ? 2 : 1;  // steps the issuers release together (pairs 2p, 2p + 1 when steps are small)
 constexpr int kPSlots = kSSlots / kPair;  // ring of the issuers' "empty" barriers
@@ -89,7 +96,7 @@ constexpr int a_slots(int np) {
   const int fit = (512 - np * kBlk) / (kG * kBlk / 2);
   return fit < kASlotsMax ? fit : kASlotsMax;
 }
-constexpr int kWSlots = 48;         // W blocks in flight: at least the blocks of a pair of steps, see the W producers
+constexpr int w_slots(int np, bool deep_x) { return (np >= 12 || !deep_x) ? 48 : 40; }  // W blocks in flight: at least the blocks of a pair of steps, see the W producers
 constexpr int kMmaWarps = 12;       // warps reserved for MMA issue (a multiple of 4); the first NP are used, one per accumulator
 constexpr int kConvSets = 2;        // converter warp sets (four warps each) that alternate steps
 constexpr int kProdWarps = 4;       // TMA-issuing warps: one for the X tiles, the others for the W blocks
@@ -99,11 +106,11 @@ constexpr int kConv1 = kMma0 + kMmaWarps;    // first warp of the second convert
 constexpr int kProd0 = kConv1 + 4;  // first producer warp
 constexpr int kThreads = 32 * (kProd0 + kProdWarps);
 static_assert(kWProd <= kSSlots, "a producer may run at most one ring turn ahead of the release it waits for");
-static_assert(kSSlots % 2 == 0 && kSSlots >= kXSlots + kASlotsMax,
+static_assert(kSSlots % 2 == 0 && kSSlots >= kXSlotsMax + kASlotsMax,
               "the X producer's arrival for step s must find the phase of step s - kSSlots complete, see there");
 static_assert(kConv1 % 4 == 0, "converter warps must map onto their tensor-memory lane quadrant");
 static_assert(kNPMax <= 12 && kNPMax <= kMmaWarps, "a step record packs 12-bit block masks; one issuer warp per accumulator");
-static_assert(kWSlots >= kPair * kG * kNPMax && kWSlots < 64,
+static_assert(w_slots(12, false) >= kPair * kG * 12 && w_slots(10, true) >= kPair * kG * 10 && w_slots(12, false) < 64,
               "the W blocks of a pair of steps must fit the ring; a ring position packs into 6 bits");
 
 struct DsdTcParams {
@@ -117,26 +124,30 @@ struct DsdTcParams {
 };
 
 constexpr uint32_t kTmemCols = 512;
-static_assert(kXSlots * kXBytes + kWSlots * kWBytes >= (kNPMax / 2) * kSubBytes,
-              "the epilogue stages the output tile in the X ring and the W ring behind it");
 
-// shared-memory carve-up (byte offsets from a 1 KB aligned base)
-constexpr int kOffX = 0;                                  // X ring   [kXSlots][128 rows x 128 B]
-constexpr int kOffW = kOffX + kXSlots * kXBytes;           // W ring   [kWSlots][2 KB]
-constexpr int kOffMask = kOffW + kWSlots * kWBytes;       // kmask    [Kb]        u32: row-blocks keeping K-block k
-constexpr int kOffSrc = kOffMask + kMaxKb * 4;            // wsrc     [Kb][NP]    u16: BCSR position within the panel
-constexpr int kOffStep = kOffSrc + kMaxKb * kNPMax * 2;      // step_kp  [steps]     u16: K-pair index
-constexpr int kOffCum = kOffStep + kMaxSteps * 2;         // cum_w    [steps + 1] u16: W blocks of all earlier steps
-constexpr int kOffWait = kOffCum + (kMaxSteps + 8) * 2;   // wait_for [steps]     s16
-constexpr int kOffRec = (kOffWait + kMaxSteps * 2 + 7) / 8 * 8;  // rec [steps] u64: 12-bit block mask per K-block | ring pos << 48
-constexpr int kOffIss = kOffRec + kMaxSteps * 8;          // iss_tab  [steps][NP][kG] u8: W ring slot of the block, 0xff = none
-constexpr int kOffBias = kOffIss + kMaxSteps * kNPMax * kG;  // bias     [NP * 32]   f32
-constexpr int kOffCtl = kOffBias + kNPMax * kBlk * 4;        // mbarriers and scalars
-constexpr int kSmemTotal = kOffCtl + 512 + 1024 /* alignment slack */;
-static_assert(kOffRec % 8 == 0 && kOffBias % 8 == 0 && kOffCtl % 8 == 0, "alignment of the shared-memory tables");
-static_assert(kSmemTotal <= 227 * 1024, "shared memory budget");
+// shared-memory carve-up (byte offsets from a 1 KB aligned base), per panel width
+template <int NP, bool DEEP_X>
+struct Lay {
+  static constexpr int kXSlots = x_slots(NP, DEEP_X), kWSlots = w_slots(NP, DEEP_X);
+  static constexpr int kOffX = 0;                                  // X ring   [kXSlots][128 rows x 128 B]
+  static constexpr int kOffW = kOffX + kXSlots * kXBytes;           // W ring   [kWSlots][2 KB]
+  static constexpr int kOffMask = kOffW + kWSlots * kWBytes;       // kmask    [Kb]        u32: row-blocks keeping K-block k
+  static constexpr int kOffSrc = kOffMask + kMaxKb * 4;            // wsrc     [Kb][NP]    u16: BCSR position within the panel
+  static constexpr int kOffStep = kOffSrc + kMaxKb * kNPMax * 2;   // step_kp  [steps]     u16: K-pair index
+  static constexpr int kOffCum = kOffStep + kMaxSteps * 2;         // cum_w    [steps + 1] u16: W blocks of all earlier steps
+  static constexpr int kOffWait = kOffCum + (kMaxSteps + 8) * 2;   // wait_for [steps]     s16
+  static constexpr int kOffRec = (kOffWait + kMaxSteps * 2 + 7) / 8 * 8;  // rec [steps] u64: 12-bit block mask per K-block | ring pos << 48
+  static constexpr int kOffIss = kOffRec + kMaxSteps * 8;          // iss_tab  [steps][NP][kG] u8: W ring slot of the block, 0xff = none
+  static constexpr int kOffBias = kOffIss + kMaxSteps * kNPMax * kG;  // bias  [NP * 32]   f32
+  static constexpr int kOffCtl = kOffBias + kNPMax * kBlk * 4;     // mbarriers and scalars
+  static constexpr int kSmemTotal = kOffCtl + 512 + 1024 /* alignment slack */;
+  static_assert(kOffRec % 8 == 0 && kOffBias % 8 == 0 && kOffCtl % 8 == 0, "alignment of the shared-memory tables");
+  static_assert(kSmemTotal <= 227 * 1024, "shared memory budget");
+  static_assert(kXSlots * kXBytes + kWSlots * kWBytes >= (kNPMax / 2) * kSubBytes,
+                "the epilogue stages the output tile in the X ring and the W ring behind it");
+};
 
-template <int FMT, int NP>
+template <int FMT, int NP, bool DEEP_X>
 __global__ void __launch_bounds__(kThreads, 1)
 bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    const __grid_constant__ CUtensorMap tm_c, DsdTcParams p) {
@@ -147,6 +158,11 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   static_assert(kASlots >= 2 && kAccCols + kASlots * kACols <= kTmemCols, "tensor memory budget");
   constexpr int kIssuers = NP;  // issuer warps in use
   constexpr uint32_t kLow = (1u << NP) - 1u;
+  using L = Lay<NP, DEEP_X>;
+  constexpr int kXSlots = L::kXSlots, kWSlots = L::kWSlots;
+  constexpr int kOffX = L::kOffX, kOffW = L::kOffW, kOffMask = L::kOffMask, kOffSrc = L::kOffSrc, kOffStep = L::kOffStep,
+                kOffCum = L::kOffCum, kOffWait = L::kOffWait, kOffRec = L::kOffRec, kOffIss = L::kOffIss,
+                kOffBias = L::kOffBias, kOffCtl = L::kOffCtl;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -450,14 +466,25 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     bool ok = true;
     for (int s = conv_set; s < n_steps; s += kConvSets) {
       const int slot = s % kXSlots, aslot = s % kASlots;
+      // the loads of the step have landed: take the first half of the tile into registers at once, so that
+      // only the stores to tensor memory follow the wait for the activation slot
+      if (!mbar_wait_warp(&full_bar[s % kSSlots], (s / kSSlots) & 1)) { ok = false; break; }
+      uint32_t r[32];
+      {
+        const uint8_t* xrow = x_ring + slot * kXBytes + row * (kSubK * 2);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((c ^ sw) << 4));
+          r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
+        }
+      }
       // the activation slot is free once the MMAs of step s - kASlots are done (this warp confirmed the
       // release of step s - kConvSets - kASlots on its previous turn, so the parity cannot alias)
       if (s >= kASlots && !mbar_wait_warp(&empty_bar[((s - kASlots) / kPair) % kPSlots], (((s - kASlots) / kPair) / kPSlots) & 1)) { ok = false; break; }
-      if (!mbar_wait_warp(&full_bar[s % kSSlots], (s / kSSlots) & 1)) { ok = false; break; }
+      tmem_st_x32(a_tmem + aslot * kACols + lane_addr, r);
 #pragma unroll
-      for (int t = 0; t < kSubTiles; ++t) {
+      for (int t = 1; t < kSubTiles; ++t) {
         const uint8_t* xrow = x_ring + slot * kXBytes + t * kSubBytes + row * (kSubK * 2);
-        uint32_t r[32];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((c ^ sw) << 4));
@@ -545,7 +572,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   }
 }
 
-template <int FMT, int NP>
+template <int FMT, int NP, bool DEEP_X>
 int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
   CUtensorMap tm_x, tm_w;
   {
@@ -579,7 +606,8 @@ int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
   q.val_stride_blocks = p.val_stride_blocks;
   q.status = device_status_ptr();
   if (!q.status) return SPARTA_ERR_DRIVER;
-  auto kern = bsmm_dsd_tc_kernel<FMT, NP>;
+  auto kern = bsmm_dsd_tc_kernel<FMT, NP, DEEP_X>;
+  constexpr int kSmemTotal = Lay<NP, DEEP_X>::kSmemTotal;
   static SmemAttrOnce attr;
   if (cudaError_t e = attr.ensure(kern, kSmemTotal); e != cudaSuccess) return static_cast<int>(e);
   dim3 grid((q.Nb + NP - 1) / NP, p.M / kTileM, p.batch);
@@ -615,11 +643,18 @@ int dsd_tc_launch(const BsmmParams& p, cudaStream_t st) {
     const long long cost = ((ctas + kNumSMs - 1) / kNumSMs) * (6 + np);
     if (best_cost < 0 || cost < best_cost) { best = np; best_cost = cost; }
   }
+  // sparse masks (few W blocks per step) take the variant with a fourth X slot, see x_slots()
+  const double density = (double)p.val_stride_blocks / ((double)(p.N / kBlk) * (double)(p.K / kBlk));
+  const bool deep_x = best <= 10 && density <= 0.15;
   const bool h = p.dtype == SPARTA_F16;
   switch (best) {
-    case 8: return h ? launch_dsd_tc<0, 8>(p, st) : launch_dsd_tc<1, 8>(p, st);
-    case 10: return h ? launch_dsd_tc<0, 10>(p, st) : launch_dsd_tc<1, 10>(p, st);
-    default: return h ? launch_dsd_tc<0, 12>(p, st) : launch_dsd_tc<1, 12>(p, st);
+    case 8:
+      if (deep_x) return h ? launch_dsd_tc<0, 8, true>(p, st) : launch_dsd_tc<1, 8, true>(p, st);
+      return h ? launch_dsd_tc<0, 8, false>(p, st) : launch_dsd_tc<1, 8, false>(p, st);
+    case 10:
+      if (deep_x) return h ? launch_dsd_tc<0, 10, true>(p, st) : launch_dsd_tc<1, 10, true>(p, st);
+      return h ? launch_dsd_tc<0, 10, false>(p, st) : launch_dsd_tc<1, 10, false>(p, st);
+    default: return h ? launch_dsd_tc<0, 12, false>(p, st) : launch_dsd_tc<1, 12, false>(p, st);
   }
 }
 

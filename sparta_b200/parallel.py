@@ -52,11 +52,13 @@ def shard_row_mask(mask: torch.Tensor, world_size: int, rank: int, block_rows: i
     return mask[lo:hi].contiguous()
 
 
-def all_gather_outputs(local: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+def all_gather_outputs(local: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Concatenate the ranks' outputs along dimension 0 (every rank gets the full tensor).
 
     Shards may differ in size along dimension 0 by one group; equal shards use a single
-    ``all_gather_into_tensor``.
+    ``all_gather_into_tensor``, into ``out`` when the caller provides the full-size buffer (no allocation
+    per call).
     """
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return local
@@ -67,7 +69,10 @@ def all_gather_outputs(local: torch.Tensor, group: Optional[dist.ProcessGroup] =
     dist.all_reduce(sizes, group=group)
     sizes = sizes.tolist()
     if len(set(sizes)) == 1:
-        out = torch.empty((world * sizes[0],) + local.shape[1:], dtype=local.dtype, device=local.device)
+        shape = (world * sizes[0],) + local.shape[1:]
+        if out is None:
+            out = torch.empty(shape, dtype=local.dtype, device=local.device)
+        assert tuple(out.shape) == shape and out.dtype == local.dtype and out.is_contiguous()
         dist.all_gather_into_tensor(out, local, group=group)
         return out
     # uneven shards: pad to the largest, gather once, drop the padding

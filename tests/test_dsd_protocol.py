@@ -1,8 +1,8 @@
 """Discrete-event simulation of the mbarrier protocol of the tcgen05 dsd kernel
 (``sparta_b200/csrc/bsmm_dsd_tc.cu``): one X producer warp, three W producer warps, two converter sets,
 one issuer warp per block column; a ring of 12 steps for the "full" barriers, X slots in shared memory
-that the converters free, activation slots in tensor memory and a ring of 48 W blocks that the issuers
-free (per step or per pair of steps); waits that name a phase by its parity only.
+that the converters free, activation slots in tensor memory and a ring of 40 or 48 W blocks that the
+issuers free (per step or per pair of steps); waits that name a phase by its parity only.
 
 The simulation runs the roles' wait / arrive sequences under random timing with the mbarrier rules
 (a wait for parity P succeeds when the barrier's current phase has the other parity; an arrival beyond
@@ -16,7 +16,7 @@ import random
 import numpy as np
 import pytest
 
-KS, KW, NWPROD = 12, 48, 3
+KS, NWPROD = 12, 3
 
 
 class Barrier:
@@ -34,7 +34,7 @@ class Barrier:
         return (self.phase & 1) != parity
 
 
-def wait_for_table(need):
+def wait_for_table(need, KW=48):
     """Latest earlier step whose W blocks still occupy the ring positions step s needs (-1: none)."""
     cum = np.concatenate([[0], np.cumsum(need)])
     table = []
@@ -47,15 +47,15 @@ def wait_for_table(need):
     return cum, table
 
 
-def simulate(need, seed, KA=3, NISS=10, KX=3, PAIR=1):
+def simulate(need, seed, KA=3, NISS=10, KX=4, PAIR=1, KW=40):
     """KA activation slots in tensor memory, NISS issuer warps (one per block column of the panel), KX
-    X slots in shared memory, PAIR steps released together by the issuers.  The kernel as built
-    (four K-blocks per step): KX 3, PAIR 1 and KA / NISS of 2 / 12, 3 / 10 or 4 / 8; its variant with two
-    K-blocks per step: KX 5, PAIR 2 and 4 / 12, 6 / 10 or 6 / 8."""
+    X slots in shared memory, PAIR steps released together by the issuers, KW W ring slots.  The kernel as
+    built (four K-blocks per step): PAIR 1 and KA / NISS / KX / KW of 2 / 12 / 3 / 48, 3 / 10 / 4 / 40 or
+    4 / 8 / 4 / 40; its variant with two K-blocks per step: KX 5, PAIR 2 and 4 / 12, 6 / 10 or 6 / 8."""
     KP = KS // PAIR
     rnd = random.Random(seed)
     n = len(need)
-    cum, wait_for = wait_for_table(need)
+    cum, wait_for = wait_for_table(need, KW)
     full = [Barrier(2, f'full{i}') for i in range(KS)]      # X producer + W producer
     empty = [Barrier(NISS, f'empty{i}') for i in range(KP)]
     pair_wait = lambda t: ('wait', empty[(t // PAIR) % KP], ((t // PAIR) // KP) & 1)  # release of step t
@@ -96,10 +96,11 @@ def simulate(need, seed, KA=3, NISS=10, KX=3, PAIR=1):
     def converter(c):
         for s in range(c, n, 2):
             xslot, aslot = s % KX, s % KA
+            yield ('wait', full[s % KS], (s // KS) & 1)   # the tile has landed: half of it goes to registers at once
+            assert x_owner[xslot] == s, f'converter of step {s} reads X slot holding {x_owner[xslot]}'
+            yield ('delay', jitter(50, 150))
             if s >= KA:
                 yield pair_wait(s - KA)
-            yield ('wait', full[s % KS], (s // KS) & 1)
-            assert x_owner[xslot] == s, f'converter of step {s} reads X slot holding {x_owner[xslot]}'
             yield ('delay', jitter(100, 400))
             assert a_owner[aslot] is None, f'A slot {aslot} of step {a_owner[aslot]} overwritten by {s}'
             a_owner[aslot] = s
@@ -154,18 +155,18 @@ def simulate(need, seed, KA=3, NISS=10, KX=3, PAIR=1):
     assert not w_owner and all(o is None for o in x_owner) and all(o is None for o in a_owner)
 
 
-# (activation slots, issuers, X slots, steps released together, K-blocks per step)
-CONFIGS = [(2, 12, 3, 1, 4), (3, 10, 3, 1, 4), (4, 8, 3, 1, 4),     # the kernel as built
-           (4, 12, 5, 2, 2), (6, 10, 5, 2, 2), (6, 8, 5, 2, 2)]     # its variant with two K-blocks per step
+# (activation slots, issuers, X slots, steps released together, K-blocks per step, W ring slots)
+CONFIGS = [(2, 12, 3, 1, 4, 48), (3, 10, 4, 1, 4, 40), (4, 8, 4, 1, 4, 40),     # the kernel as built
+           (4, 12, 5, 2, 2, 48), (6, 10, 5, 2, 2, 48), (6, 8, 5, 2, 2, 48)]     # its variant with two K-blocks per step
 
 
-@pytest.mark.parametrize('ka,niss,kx,pair,kg', CONFIGS)
+@pytest.mark.parametrize('ka,niss,kx,pair,kg,kw', CONFIGS)
 @pytest.mark.parametrize('density', [0.02, 0.1, 0.25, 0.5, 1.0])
-def test_protocol_under_random_timing(density, ka, niss, kx, pair, kg):
+def test_protocol_under_random_timing(density, ka, niss, kx, pair, kg, kw):
     rs = np.random.RandomState(int(density * 1000) + ka)
     for trial in range(6):
         need = np.maximum(1, rs.binomial(kg * niss, density, size=rs.randint(1, 100)))
-        simulate(need, seed=trial, KA=ka, NISS=niss, KX=kx, PAIR=pair)
+        simulate(need, seed=trial, KA=ka, NISS=niss, KX=kx, PAIR=pair, KW=kw)
 
 
 def test_wait_for_table_small_case():

@@ -107,3 +107,22 @@ def test_band_global_random_mask_density():
     occ = oracle.block_occupancy(m.numpy(), 64, 64)
     assert occ[0].all() and occ[:, 0].all()
     assert 1150 < occ.sum() < 1400  # ~1286 of 4096 blocks
+
+
+@pytest.mark.parametrize('mode', ['sdd', 'dsd', 'dds'])
+@pytest.mark.parametrize('trans_A', [False, True])
+@pytest.mark.parametrize('trans_B', [False, True])
+def test_matmul_reference_matches_the_reference_method(mode, trans_A, trans_B):
+    """``oracle.matmul_reference`` against vectors produced by ``SparseMatMulKernel.reference`` itself
+    (extracted from the reference's class by tests/golden/make_golden.py).  Before ``compile`` the reference
+    multiplies a dds output by the element mask -- a block coverage with 1 x 1 blocks -- and after it by the
+    coverage of the kernel's BM x BN blocks."""
+    g = np.load(os.path.join(GOLDEN, 'matmul.npz'))
+    batch, M, K, N, BM, BN = g['shape'].tolist()
+    key = f'{mode}_{int(trans_A)}{int(trans_B)}'
+    A, B, bias, mask = (torch.from_numpy(g[f'{key}_{n}']) for n in ('A', 'B', 'bias', 'mask'))
+    for biased in (False, True):
+        for ready, block in ((False, (1, 1)), (True, (BM, BN))):
+            got = oracle.matmul_reference(A, B, bias if biased else None, mask, mode, trans_A, trans_B, block)
+            want = torch.from_numpy(g[f'{key}_C_b{int(biased)}_r{int(ready)}'])
+            torch.testing.assert_close(got, want, rtol=1e-6, atol=1e-6)

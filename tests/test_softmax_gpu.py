@@ -108,3 +108,34 @@ def test_half_types_block_uniform_mask(dtype):
     assert ix.block_uniform
     out = ix.inverse(op(ix.convert(x.cuda()))).float().cpu()
     torch.testing.assert_close(out, oracle.softmax_forward_reference(x.float(), mask, 2.0), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('compressed', [True, False])
+def test_half_types_element_mask(dtype, compressed):
+    """fp16 / bf16 with a mask finer than the block (8 x 8 inside 64 x 64 blocks, some rows fully masked
+    inside kept blocks): the vector kernel overwrites masked values of the packed row before the maximum,
+    and the backward pass sees the same element mask."""
+    g = torch.Generator().manual_seed(6)
+    x = (torch.randn((2, 256, 512), generator=g) * 3).to(dtype)
+    grad = torch.randn((2, 256, 512), generator=g).to(dtype)
+    mask = oracle.block_mask((256, 512), (8, 8), 0.6, generator=g)
+    mask[72:80] = 0
+    op = SparseSoftmax(mask.cuda(), 2.0, compressed=compressed)
+    op.build({'forward:y': params(64, 64), 'backward:x': params(64, 64)}, sample_inputs=[x.cuda()])
+    ix = op.get_sparse_indexes('y')
+    assert not ix.block_uniform
+    xin, gin = x.cuda(), grad.cuda()
+    if compressed:
+        xin, gin = ix.convert(xin), ix.convert(gin)
+    xin.requires_grad_()
+    out = op(xin)
+    out.backward(gin)
+    got_y, got_dx = out.detach(), xin.grad
+    if compressed:
+        got_y, got_dx = ix.inverse(got_y), ix.inverse(got_dx)
+    want_y = oracle.softmax_forward_reference(x.float(), mask, 2.0)
+    want_dx = oracle.softmax_backward_reference(grad.float(), want_y, mask, 2.0)
+    torch.testing.assert_close(got_y.float().cpu(), want_y, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(got_dx.float().cpu(), want_dx, rtol=2e-2, atol=2e-2)
+    assert torch.all(got_y[:, 72:80] == 0)
