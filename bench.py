@@ -348,6 +348,30 @@ def run_extras(device, peaks, flush, only=None):
     except Exception as e:
         extras['attention_b4h16s4096d64'] = {'error': repr(e)[:200]}
 
+    # one rank's share of the large attention configuration at 1/32 of its head count: bf16, 64 heads, S 8192,
+    # D 128 (403 MB of q, k, v, o): the case the kernel with two Q tiles per CTA is profiled on
+    try:
+        if not want('attention_d128'):
+            raise KeyError('skipped')
+        heads, S, D = 64, 8192, 128
+        dg = torch.Generator(device=device).manual_seed(2026)
+        q, k, v = (torch.randn((heads, S, D), generator=dg, device=device, dtype=torch.bfloat16) for _ in range(3))
+        amask = oracle.band_global_random_mask(S, S, 64, 8, 0.05, seed=0).to(device)
+        attn = sparta.nn.SparseAttention(mask=amask)
+        mm = {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': 64, 'BLOCK_SIZE_K_VALUE': 64, 'BLOCK_SIZE_N_VALUE': 64}
+        sm = {'_impl': 'sparta', 'BLOCK_SIZE_H_VALUE': 64, 'BLOCK_SIZE_W_VALUE': 64, 'ROW_TILE_VALUE': 4}
+        attn.build({'qk/forward:C': mm, 'sm/forward:y': sm, 'out/forward:C': mm}, sample_inputs=[q, k, v])
+        nnz = attn.get_sparse_indexes().block_nnz
+        with torch.no_grad():
+            ms = timed(lambda: attn(q, k, v), steps=5)
+        flops = 4.0 * heads * nnz * 64 * 64 * D
+        extras['attention_h64s8192d128_bf16'] = {
+            'fwd_ms': round(ms, 4), 'nnz_blocks': nnz, 'fused': bool(attn._use_fused),
+            'tflops': round(flops / ms / 1e9, 2), 'frac_tensor_peak': round(flops / ms / 1e9 / peaks['tflops'], 4)}
+        del q, k, v, attn
+    except Exception as e:
+        extras['attention_h64s8192d128_bf16'] = {'error': repr(e)[:200]}
+
     # stand-alone SparseSoftmax forward on compressed scores of the same attention mask (the fused kernel
     # above never materialises them; this is the operator the unfused composition and the API expose)
     try:
@@ -587,7 +611,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-extras', action='store_true')
     ap.add_argument('--extras', default=None,
-                    help='comma list of extra measurements to run: linear,dense,attention,attention_c5,softmax,convert,readme,ref_gpu (default: all of these), refgrid (only when named)')
+                    help='comma list of extra measurements to run: linear,dense,attention,attention_d128,attention_c5,softmax,convert,readme,ref_gpu (default: all of these), refgrid (only when named)')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
 
@@ -677,7 +701,8 @@ def main():
     parity = None
     if rank == 0:
         want = torch.nn.functional.linear(wl['x'][:512].float(), wl['w'].float(), wl['b'].float())
-        got = wl['fn']()[:512].float().cpu()
+        with torch.no_grad():
+            got = wl['fn']()[:512].float().cpu()
         parity = {'max_abs_err': float((got - want).abs().max()), 'tolerance': 2e-2,
                   'checked': 'first 512 token rows of the device-resident headline output against F.linear in fp32 on the host; '
                              'the end-to-end output was checked against the device-resident one'}

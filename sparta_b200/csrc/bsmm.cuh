@@ -40,6 +40,13 @@ inline int bsmm_tc(const BsmmParams& p, cudaStream_t st) {
   return p.mode == MODE_DDS ? dds_tc_launch(p, st) : dsd_tc_launch(p, st);
 }
 
+// fused attention with two Q tiles per CTA (attn_tc2.cu): query lengths that are a multiple of 256
+bool attn_tc2_supported(int Nt);
+bool kv_exceeds_l2(int heads, int Ns, int D);
+int attn_tc2_launch(const void* Q, const void* K, const void* V, void* O, const int32_t* row_ptr,
+                    const int32_t* bcsr_idx, const uint8_t* mask, float scale_log2, int heads, int Nt, int Ns,
+                    int D, int dtype, float* lse, int32_t* status, cudaStream_t st);
+
 // whether the tcgen05 matmul / fused attention kernels are compiled into this build
 bool bsmm_tc_available();
 bool attn_tc_available();

@@ -147,29 +147,6 @@ __global__ void __launch_bounds__(128, 9) softmax_fwd_vec_kernel(SmParams p) {
     return;
   }
   const float scale2 = p.scale * 1.4426950408889634f;
-#ifndef SPARTA_SOFTMAX_NO_PREFETCH
-  // A warp has loads in flight only while it fetches its own row, about a third of its time, which leaves
-  // too few bytes in flight to cover the latency of HBM.  So every warp also asks L2 for the row that the
-  // CTA `kPrefetchCtas` further on in launch order will read (about one wave of CTAs ahead): by the time
-  // that CTA runs, its loads find the lines in L2.  One 128-byte line per lane and instruction.
-  if (p.compressed) {
-    constexpr int kPrefetchCtas = 148 * 9;
-    long long cta = (long long)blockIdx.y * gridDim.x + blockIdx.x + kPrefetchCtas;
-    const long long b2 = cta / gridDim.x;
-    const int row2 = static_cast<int>(cta - b2 * gridDim.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (b2 < gridDim.y && row2 < p.H) {
-      const int br2 = row2 / p.BH, y2 = row2 - br2 * p.BH;
-      const int u0 = p.row_ptr[br2], u1 = p.row_ptr[br2 + 1];
-      const T* x2 = static_cast<const T*>(p.x) + b2 * bstride;
-      const int lines_per_block = max(1, static_cast<int>(p.BW * sizeof(T)) / 128);
-      for (int i = lane; i < (u1 - u0) * lines_per_block; i += 32) {
-        const int t = u0 + i / lines_per_block, part = i - (i / lines_per_block) * lines_per_block;
-        const T* addr = x2 + ((long long)t * p.BH + y2) * p.BW + part * (128 / sizeof(T));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(addr));
-      }
-    }
-  }
-#endif
   uint32_t off[kVecs];  // within one batch slice (the host checks that a slice has fewer than 2^32 elements)
   uint4 raw[kVecs];  // the row's values stay packed in their own type: 32 registers, so four CTAs fit an SM
 #pragma unroll

@@ -169,3 +169,13 @@ def test_default_fused_setting_trains(dtype):
         fused_out = op(qc, kc, vc)
     assert op.fused_status() == [0, 0, 0, 0]
     torch.testing.assert_close(fused_out.float().cpu(), target.detach(), **tol)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('E', [64, 128])
+def test_fused_attention_odd_tile_count(dtype, E):
+    """384 query rows = three 128-row tiles: with a head dimension of 128 the kernel with two Q tiles per CTA
+    does not apply (it wants a multiple of 256 rows) and the one-tile kernel runs; both must agree with the oracle."""
+    g = torch.Generator().manual_seed(21)
+    mask = oracle.block_mask((384, 640), (64, 64), 0.5, generator=g)
+    _fused_case(dtype, E, 3, 384, 640, mask, seed=22)
