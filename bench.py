@@ -326,6 +326,46 @@ def run_extras(device, peaks, flush, only=None):
             except Exception as e:  # an extra must not take the headline number down
                 extras[f'linear_{mode}_{int(sp * 100)}'] = {'error': repr(e)[:200]}
 
+    # SparseLinear training step at 75 % (forward, input gradient = dsd with the BCSC weight, weight gradient = dds
+    # with A stored [K, M]), all three on tcgen05 tiles, beside the same step on the FMA tiles
+    try:
+        if not want('linear_train'):
+            raise KeyError('skipped')
+        x, w, b, mask = linear_inputs(SPARSITY)
+        gy = torch.randn((TOKENS, OUT_F), generator=torch.Generator().manual_seed(5)).half().to(device)
+        rec = {}
+        for fam, tiles in (('tcgen05', ((128, 32, 32), (128, 32, 32), (32, 64, 32))),
+                           ('simt', ((64, 32, 32), (64, 32, 32), (32, 64, 32)))):
+            dense = torch.nn.Linear(IN_F, OUT_F, device=device, dtype=torch.float16)
+            dense.load_state_dict({'weight': w.to(device), 'bias': b.to(device)})
+            op = sparta.nn.SparseLinear(dense, weight_mask=mask.to(device))
+            xd = x.to(device).requires_grad_(True)
+            op.build({name: {'_impl': 'sparta', '_family': fam, 'BLOCK_SIZE_M_VALUE': t[0], 'BLOCK_SIZE_K_VALUE': t[1],
+                             'BLOCK_SIZE_N_VALUE': t[2]}
+                      for name, t in zip(('forward:C', 'backward:A', 'backward:B'), tiles)}, sample_inputs=[xd.detach()])
+            nnz = op.get_sparse_indexes('B').block_nnz
+
+            def step():
+                xd.grad = None
+                op.weight.grad = None
+                op(xd).backward(gy)
+            ms = timed(step)
+            ctx = op._sparse_ctx
+            wv = op.weight.detach().unsqueeze(0)
+            parts = {'fwd_ms': timed(lambda: ctx.forward_C(xd.detach().unsqueeze(0), wv, op.bias.detach().unsqueeze(0))),
+                     'dgrad_ms': timed(lambda: ctx.backward_A(gy.unsqueeze(0), wv)),
+                     'wgrad_ms': timed(lambda: ctx.backward_B(gy.unsqueeze(0), xd.detach().unsqueeze(0)))}
+            tf = 3 * 2.0 * TOKENS * BLOCK * BLOCK * nnz / ms / 1e9
+            rec[fam] = {'step_ms': round(ms, 4), **{k: round(v, 4) for k, v in parts.items()}, 'tflops': round(tf, 2),
+                        'frac_tensor_peak': round(tf / peaks['tflops'], 4)}
+            del op, dense
+        rec['nnz_blocks'] = nnz
+        extras['linear_train_75'] = rec
+    except KeyError:
+        pass
+    except Exception as e:
+        extras['linear_train_75'] = {'error': repr(e)[:200]}
+
     # fused sparse attention forward: B4 H16 S4096 D64 fp16, band + global + 5 % random 64x64 blocks
     try:
         if not want('attention'):
@@ -611,7 +651,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-extras', action='store_true')
     ap.add_argument('--extras', default=None,
-                    help='comma list of extra measurements to run: linear,dense,attention,attention_d128,attention_c5,softmax,convert,readme,ref_gpu (default: all of these), refgrid (only when named)')
+                    help='comma list of extra measurements to run: linear,linear_train,dense,attention,attention_d128,attention_c5,softmax,convert,readme,ref_gpu (default: all of these), refgrid (only when named)')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
 

@@ -157,10 +157,13 @@ int sparta_bcs_sum(const void* vals, void* out, const int32_t* row_ptr, const in
  * impl              SPARTA_IMPL_*; AUTO uses the tile table.  grid_blocks_hint bounds the dds grid
  *                   (pass idx_capacity or the host's nnz if known; <= 0 lets the library choose).
  * SPARTA_IMPL_TCGEN05 covers, for fp16 / bf16 (fp32 accumulation):
- *   dsd  trans_a = 0, trans_b = 1, compressed = 1, 32-bit BCSR, BM = 128, BK = BN = 32, M % 128 == 0,
- *        K <= 8192, one index set (the SparseLinear weight layout);
- *   dds  trans_a = 0, 32-bit BCSR, BM = BN = 32, BK = 64, M % 128 == 0, N <= 32768, compressed or
- *        dense output, one index set or one per batch element;
+ *   dsd  trans_a = 0, compressed = 1, BM = 128, BK = BN = 32, M % 128 == 0, K <= 8192, one index set:
+ *        trans_b = 1 with the 32-bit BCSR (the SparseLinear weight layout) or trans_b = 0 with the BCSC,
+ *        32- or 64-bit (its input gradient);
+ *   sdd  trans_b = 1, compressed = 1, BM = BK = 32, BN = 128, N % 128 == 0, K <= 8192, one index set:
+ *        trans_a = 0 with the 32-bit BCSR or trans_a = 1 with the BCSC, 32- or 64-bit;
+ *   dds  either trans_a, either trans_b, 32-bit BCSR, BM = BN = 32, BK = 64, M % 128 == 0, N <= 32768,
+ *        compressed or dense output, one index set or one per batch element;
  * and returns SPARTA_ERR_UNSUPPORTED otherwise.  SPARTA_IMPL_SIMT (and AUTO outside that coverage)
  * takes every mode, transposition and dtype with CTA tiles 4 .. 64 per dimension.
  */

@@ -95,8 +95,9 @@ extern "C" int sparta_tile_table(int op, int dtype, sparta_tile_entry* out, int 
   if (op <= 2) {
     // tcgen05 entries first: they are the preferred choice where they apply
     if (dtype != SPARTA_F32 && bsmm_tc_available()) {
-      if (op == 1) emit({op, dtype, SPARTA_IMPL_TCGEN05, 128, 32, 32, 0, 1, 1});
-      if (op == 2) emit({op, dtype, SPARTA_IMPL_TCGEN05, 32, 64, 32, 0, 1, 1});
+      if (op == 0) emit({op, dtype, SPARTA_IMPL_TCGEN05, 32, 32, 128, -1, 1, 1});
+      if (op == 1) emit({op, dtype, SPARTA_IMPL_TCGEN05, 128, 32, 32, 0, -1, 1});
+      if (op == 2) emit({op, dtype, SPARTA_IMPL_TCGEN05, 32, 64, 32, -1, -1, -1});
     }
     for (int bm : kSimtSizes)
       for (int bk : kSimtSizes)

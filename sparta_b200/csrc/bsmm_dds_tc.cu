@@ -8,7 +8,8 @@
 // with the B operand GATHERED column block by column block through TMA, and its epilogue writes only
 // the kept 32 x 32 blocks (compressed BCSR order or dense).  At 90 % block sparsity about two thirds of
 // the block columns of a row tile are skipped entirely.
-//   warp 4    producer: A tile [128, 64] by coordinate, B tiles [32, 64] of the group's columns
+//   warp 4    producer: A tile [128, 64] by coordinate (four [64, 32] boxes when A is stored [K, M]), B tiles
+//             [32, 64] of the group's columns
 //   warp 5    one thread issues four tcgen05.mma per 64-wide K chunk and commits
 //   warps 0-3 epilogue: warp w holds block row w of the tile (TMEM lanes 32w .. 32w+31)
 // Replaces sparta_sparse_matmul_dds.cuh.j2 / openai_sparse_matmul_dds.cuh.j2 for these layouts.
@@ -44,7 +45,7 @@ struct DdsTcParams {
   const void* bias;
   void* C;
   int M, N, K, Nb;
-  int compressed, trans_b;
+  int compressed, trans_a, trans_b;
   int n_index_sets;
   long long ptr_stride, idx_stride, val_stride_blocks;
   int32_t* status;
@@ -142,8 +143,12 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       uint8_t* st = stages + s * kStageBytes;
       if (lane == 0) {
         mbar_arrive_expect_tx(&full_bar[s], kABytes + ncols * kBBlockBytes);
-        tma_load_2d(st, &tm_a, c * kChunkK, batch * p.M + tile * kTileM, &full_bar[s]);
+        if (!p.trans_a) tma_load_2d(st, &tm_a, c * kChunkK, batch * p.M + tile * kTileM, &full_bar[s]);
       }
+      __syncwarp();  // the expected byte count is registered before any lane's load can complete
+      if (p.trans_a && lane >= 16 && lane < 20)  // A stored [K, M]: the tile's four block rows, 32 rows contiguous per K row
+        tma_load_2d(st + (lane - 16) * kBBlockBytes, &tm_a, tile * kTileM + (lane - 16) * kBlk, batch * p.K + c * kChunkK,
+                    &full_bar[s]);
       if (lane < ncols) {
         uint8_t* dst = st + kABytes + lane * kBBlockBytes;
         if (p.trans_b) tma_load_2d(dst, &tm_b, c * kChunkK, batch * p.N + col * kBlk, &full_bar[s]);
@@ -156,11 +161,13 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     // ------------------------------ MMA issue ------------------------------
     // A: K-major, 128-byte swizzle.  B: K-major 128-byte swizzle when stored [N, K]; MN-major 64-byte
     // swizzle when stored [K, N] (32 columns contiguous per K row, column blocks 4 KB apart).
-    const uint64_t a_hi = make_smem_desc(0, 16, 1024, SW_128B);
+    // A stored [K, M] is the mirror of B stored [K, N]: MN-major, block rows 4 KB apart.
+    const uint64_t a_hi = p.trans_a ? make_smem_desc(0, kBBlockBytes, 512, SW_64B) : make_smem_desc(0, 16, 1024, SW_128B);
+    const uint32_t a_step = p.trans_a ? (16u * 64u) >> 4 : 2u;
     const uint64_t b_hi = p.trans_b ? make_smem_desc(0, 16, 1024, SW_128B)
                                     : make_smem_desc(0, kBBlockBytes, 512, SW_64B);
     const uint32_t b_step = p.trans_b ? 2u : (16u * 64u) >> 4;  // 16 K elements, in 16-byte units
-    const uint32_t idesc = make_idesc_f16(kTileM, kBlk * ncols, FMT, 0, p.trans_b ? 0 : 1);
+    const uint32_t idesc = make_idesc_f16(kTileM, kBlk * ncols, FMT, p.trans_a ? 1 : 0, p.trans_b ? 0 : 1);
     const uint32_t base = smem_u32(stages) >> 4;
     bool ok = true;
     for (int c = 0; c < nchunks; ++c) {
@@ -172,7 +179,7 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         const uint32_t b_lo = a_lo + (kABytes >> 4);
 #pragma unroll
         for (int kk = 0; kk < kChunkK / 16; ++kk)
-          umma_ss(tmem_base, a_hi | (a_lo + 2 * kk), b_hi | (b_lo + b_step * kk), idesc, (c | kk) ? 1u : 0u);
+          umma_ss(tmem_base, a_hi | (a_lo + a_step * kk), b_hi | (b_lo + b_step * kk), idesc, (c | kk) ? 1u : 0u);
         umma_commit(&empty_bar[s]);
       }
       __syncwarp();
@@ -252,7 +259,13 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
 template <int FMT, int STAGES>
 int launch_dds(const BsmmParams& p, cudaStream_t st) {
   CUtensorMap tm_a, tm_b;
-  {
+  if (p.trans_a) {
+    const uint64_t dims[2] = {(uint64_t)p.M, (uint64_t)p.batch * p.K};
+    const uint64_t strides[1] = {(uint64_t)p.M * 2};
+    const uint32_t box[2] = {kBlk, kChunkK};
+    int rc = make_tensor_map(&tm_a, p.A, p.dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc != SPARTA_OK) return rc;
+  } else {
     const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.batch * p.M};
     const uint64_t strides[1] = {(uint64_t)p.K * 2};
     const uint32_t box[2] = {kChunkK, kTileM};
@@ -278,7 +291,7 @@ int launch_dds(const BsmmParams& p, cudaStream_t st) {
   q.bias = p.bias;
   q.C = p.C;
   q.M = p.M; q.N = p.N; q.K = p.K; q.Nb = p.N / kBlk;
-  q.compressed = p.compressed; q.trans_b = p.trans_b;
+  q.compressed = p.compressed; q.trans_a = p.trans_a; q.trans_b = p.trans_b;
   q.n_index_sets = p.n_index_sets;
   q.ptr_stride = p.ptr_stride; q.idx_stride = p.idx_stride; q.val_stride_blocks = p.val_stride_blocks;
   q.status = device_status_ptr();
@@ -310,7 +323,7 @@ int launch_dds(const BsmmParams& p, cudaStream_t st) {
 }  // namespace
 
 bool dds_tc_supported(const BsmmParams& p) {
-  if (p.mode != MODE_DDS || p.trans_a || p.idx_is_64 || !p.ptr) return false;
+  if (p.mode != MODE_DDS || p.idx_is_64 || !p.ptr) return false;
   if (p.dtype != SPARTA_F16 && p.dtype != SPARTA_BF16) return false;
   if (p.BM != kBlk || p.BN != kBlk || p.BK != kChunkK) return false;
   if (p.M % kTileM || p.N % kBlk || p.K % kChunkK || p.N / kBlk > kMaxNb) return false;
@@ -318,7 +331,7 @@ bool dds_tc_supported(const BsmmParams& p) {
   if ((long long)p.batch * p.M > 0x7fffffffll || (long long)p.batch * p.N > 0x7fffffffll ||
       (long long)p.batch * p.K > 0x7fffffffll || p.batch > 65535 || p.M / kTileM > 65535)
     return false;
-  if (!aligned(p.A, 16) || !aligned(p.B, 16) || !aligned(p.C, 16) || (p.K * 2) % 16 || (p.N * 2) % 16) return false;
+  if (!aligned(p.A, 16) || !aligned(p.B, 16) || !aligned(p.C, 16) || (p.K * 2) % 16 || (p.N * 2) % 16 || (p.M * 2) % 16) return false;
   return true;
 }
 

@@ -55,7 +55,17 @@
 //                store per tile of 64 output columns, issued as soon as the tile's four warps are done
 // Every mbarrier wait is bounded; a wait that runs out sets a status word and the CTA winds down.
 //
-// Replaces sparta_sparse_matmul_dsd.cuh.j2 / openai_sparse_matmul_dsd.cuh.j2 for this layout.
+// Layouts.  The same kernel serves every product that has this shape -- a dense operand with the reduction
+// dimension contiguous, times a block-sparse operand indexed along the output dimension:
+//   dsd, B stored [N, K] (BCSR by row-block n)      the SparseLinear forward;
+//   dsd, B stored [K, N] (BCSC by column-block n)   its input gradient dX = dY W: the 32 x 32 block then has the
+//                                                   output dimension contiguous and enters the MMA as an
+//                                                   MN-major B operand; with both index forms built, the
+//                                                   64-bit BCSC entries carry the value position (BCSR order);
+//   sdd with B stored [N, K]                        C^T = B A^T: the dense B plays the activations, the sparse
+//                                                   A (BCSR [M, K] or BCSC [K, M]) the weight, and the
+//                                                   epilogue stores the accumulators transposed.
+// Replaces sparta_sparse_matmul_{dsd,sdd}.cuh.j2 / openai_sparse_matmul_{dsd,sdd}.cuh.j2 for these layouts.
 #include <type_traits>
 
 #include "bsmm.cuh"
@@ -114,8 +124,11 @@ static_assert(w_slots(12, false) >= kPair * kG * 12 && w_slots(10, true) >= kPai
               "the W blocks of a pair of steps must fit the ring; a ring position packs into 6 bits");
 
 struct DsdTcParams {
-  const int32_t* row_ptr;
-  const int32_t* idx;
+  const int32_t* row_ptr;  // pointer array along the output dimension (row_ptr of [N, K], col_ptr of [K, N])
+  const void* idx;         // packed entries (output block << 16) | reduction block; 64-bit with the value position on top
+  int idx64;               // entries are 64-bit (both index forms built): values sit at entry >> 32
+  int b_mn;                // the sparse blocks have the output dimension contiguous (stored [K, N]): MN-major B operand
+  int out_t;               // store the accumulators transposed: C is [N, M] in this kernel's terms (sdd through B A^T)
   const void* bias;
   void* C;
   int M, N, Kb, Nb;
@@ -132,13 +145,13 @@ struct Lay {
   static constexpr int kOffX = 0;                                  // X ring   [kXSlots][128 rows x 128 B]
   static constexpr int kOffW = kOffX + kXSlots * kXBytes;           // W ring   [kWSlots][2 KB]
   static constexpr int kOffMask = kOffW + kWSlots * kWBytes;       // kmask    [Kb]        u32: row-blocks keeping K-block k
-  static constexpr int kOffSrc = kOffMask + kMaxKb * 4;            // wsrc     [Kb][NP]    u16: BCSR position within the panel
-  static constexpr int kOffStep = kOffSrc + kMaxKb * kNPMax * 2;   // step_kp  [steps]     u16: K-pair index
+  static constexpr int kOffSrc = kOffMask + kMaxKb * 4;            // wsrc     [Kb][NP]    u32: position of the block in the value array
+  static constexpr int kOffStep = kOffSrc + kMaxKb * NP * 4;       // step_kp  [steps]     u16: K-pair index
   static constexpr int kOffCum = kOffStep + kMaxSteps * 2;         // cum_w    [steps + 1] u16: W blocks of all earlier steps
   static constexpr int kOffWait = kOffCum + (kMaxSteps + 8) * 2;   // wait_for [steps]     s16
   static constexpr int kOffRec = (kOffWait + kMaxSteps * 2 + 7) / 8 * 8;  // rec [steps] u64: 12-bit block mask per K-block | ring pos << 48
   static constexpr int kOffIss = kOffRec + kMaxSteps * 8;          // iss_tab  [steps][NP][kG] u8: W ring slot of the block, 0xff = none
-  static constexpr int kOffBias = kOffIss + kMaxSteps * kNPMax * kG;  // bias  [NP * 32]   f32
+  static constexpr int kOffBias = (kOffIss + kMaxSteps * NP * kG + 7) / 8 * 8;  // bias  [NP * 32]   f32
   static constexpr int kOffCtl = kOffBias + kNPMax * kBlk * 4;     // mbarriers and scalars
   static constexpr int kSmemTotal = kOffCtl + 512 + 1024 /* alignment slack */;
   static_assert(kOffRec % 8 == 0 && kOffBias % 8 == 0 && kOffCtl % 8 == 0, "alignment of the shared-memory tables");
@@ -169,7 +182,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   uint8_t* x_ring = smem + kOffX;
   uint8_t* w_ring = smem + kOffW;
   uint32_t* kmask = reinterpret_cast<uint32_t*>(smem + kOffMask);
-  uint16_t* wsrc = reinterpret_cast<uint16_t*>(smem + kOffSrc);
+  uint32_t* wsrc = reinterpret_cast<uint32_t*>(smem + kOffSrc);
   uint16_t* step_kp = reinterpret_cast<uint16_t*>(smem + kOffStep);
   uint16_t* cum_w = reinterpret_cast<uint16_t*>(smem + kOffCum);
   int16_t* wait_for = reinterpret_cast<int16_t*>(smem + kOffWait);
@@ -199,7 +212,17 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   // the rows of a panel are consecutive in the BCSR array; every thread reads the panel's range and its
   // first entry now, so that the two dependent trips to memory overlap the set-up below
   const int e0 = __ldg(p.row_ptr + nb0), e1 = __ldg(p.row_ptr + nb_end);
-  const int v_first = e0 + static_cast<int>(threadIdx.x) < e1 ? __ldg(p.idx + e0 + threadIdx.x) : 0;
+  auto load_entry = [&](int e, uint32_t& pos) -> int {  // packed (output block << 16) | reduction block, and where its values sit
+    if (p.idx64) {
+      const long long w = __ldg(static_cast<const long long*>(p.idx) + e);
+      pos = static_cast<uint32_t>(w >> 32);
+      return static_cast<int>(w & 0xffffffffll);
+    }
+    pos = static_cast<uint32_t>(e);
+    return __ldg(static_cast<const int32_t*>(p.idx) + e);
+  };
+  uint32_t pos_first = 0;
+  const int v_first = e0 + static_cast<int>(threadIdx.x) < e1 ? load_entry(e0 + threadIdx.x, pos_first) : 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSSlots; ++s) mbar_init(&full_bar[s], 2);  // the X producer and the step's W producer
     for (int s = 0; s < kPSlots; ++s) mbar_init(&empty_bar[s], kIssuers);
@@ -216,7 +239,8 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   if (warp == kMma0) tmem_alloc<kTmemCols>(tmem_holder);
   for (int k = threadIdx.x; k < kG * n_pairs; k += kThreads) kmask[k] = 0;  // includes the pad blocks of the last group
   {
-    const T* bias = p.bias ? static_cast<const T*>(p.bias) + (long long)batch * p.N : nullptr;
+    // (with the transposed store the bias runs along this kernel's rows and is added in the epilogue)
+    const T* bias = p.bias && !p.out_t ? static_cast<const T*>(p.bias) + (long long)batch * p.N : nullptr;
     for (int j = threadIdx.x; j < NP * kBlk; j += kThreads) {
       const int n = nb0 * kBlk + j;
       s_bias[j] = (bias && n < p.N) ? to_float(bias[n]) : 0.f;
@@ -225,11 +249,12 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   __syncthreads();
   // entry = (row-block << 16) | K-block
   for (int e = e0 + threadIdx.x; e < e1; e += kThreads) {
-    const int v = e == e0 + static_cast<int>(threadIdx.x) ? v_first : __ldg(p.idx + e);
+    uint32_t pos = pos_first;
+    const int v = e == e0 + static_cast<int>(threadIdx.x) ? v_first : load_entry(e, pos);
     const int k = v & 0xffff, l = (v >> 16) - nb0;
     if (k < p.Kb && l >= 0 && l < NP) {  // index arrays come from the caller: never index shared memory with them unchecked
       atomicOr(&kmask[k], 1u << l);
-      wsrc[k * NP + l] = static_cast<uint16_t>(e - e0);
+      wsrc[k * NP + l] = pos;
     }
   }
   __syncthreads();
@@ -347,7 +372,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     // ------------------------------ W producers ------------------------------
     // One instruction per pair of K-blocks; lanes 0 .. NP-1 fetch the blocks of the pair's first
     // K-block, lanes 16 .. 16+NP-1 those of the second
-    const long long wrow0 = ((long long)batch * p.val_stride_blocks + e0) * kBlk;  // row in the [blocks * 32, 32] view
+    const long long wrow0 = (long long)batch * p.val_stride_blocks * kBlk;  // row in the [blocks * 32, 32] view
     const int half = lane >> 4, l = lane & 15;
     bool ok = true;
     for (int s = warp - kProd0 - 1; s < n_steps; s += kWProd) {
@@ -355,11 +380,12 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       const uint64_t r = rec[s];
       const int c0 = static_cast<int>(r >> 48) & 0x3f, wf = wait_for[s];
       uint32_t pack[kSubTiles];  // per pair of K-blocks: one bit per lane that has a block to fetch
-      int src[kSubTiles], n_blocks = 0;
+      uint32_t src[kSubTiles];
+      int n_blocks = 0;
 #pragma unroll
       for (int t = 0; t < kSubTiles; ++t) {
         pack[t] = (static_cast<uint32_t>(r >> (2 * t * NP)) & kLow) | ((static_cast<uint32_t>(r >> ((2 * t + 1) * NP)) & kLow) << 16);
-        src[t] = ((pack[t] >> lane) & 1u) ? wsrc[(kG * kp + 2 * t + half) * NP + l] : 0;
+        src[t] = ((pack[t] >> lane) & 1u) ? wsrc[(kG * kp + 2 * t + half) * NP + l] : 0u;
         n_blocks += __popc(pack[t]);
       }
       // An mbarrier wait names a phase by its parity only, so a waiter must know that the barrier is
@@ -392,9 +418,12 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   } else if (warp >= kMma0 && warp < kMma0 + kIssuers) {  // (warps up to kConv1 are spare when NP < 12)
     // ------------------------------ MMA issue ------------------------------
     // Operand addresses derive from the schedule only, so they stay warp-uniform; one lane issues.
-    constexpr uint32_t idesc = make_idesc_f16(kTileM, kBlk, FMT, 0, 0);
+    // K-major B (block stored [n][k]): K = 16 slabs 32 bytes apart inside the 64-byte rows.  MN-major B (block stored
+    // [k][n]): 16 rows of 64 bytes per slab, 1 KB apart; eight-row groups 512 bytes apart either way.
+    const uint32_t idesc = make_idesc_f16(kTileM, kBlk, FMT, 0, p.b_mn ? 1 : 0);
+    const uint32_t slab = p.b_mn ? (16u * kBlk * 2u) >> 4 : 2u;
     const uint32_t w_base16 = smem_u32(w_ring) >> 4;
-    const uint64_t desc_hi = make_smem_desc(0, 16, 512, SW_64B);
+    const uint64_t desc_hi = p.b_mn ? make_smem_desc(0, kWBytes, 512, SW_64B) : make_smem_desc(0, 16, 512, SW_64B);
     const bool leader = lane == 0;
     const int l = warp - kMma0;                        // the accumulator issued by this warp
     const uint32_t d_tmem = tmem_base + l * kBlk;
@@ -412,7 +441,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           const uint32_t a_addr = a_tmem + as * kACols + j * (kBlk / 2);
           const uint32_t b_lo = w_base16 + b * (kWBytes >> 4);
           umma_ts(d_tmem, a_addr, desc_hi | b_lo, idesc, accumulate);
-          umma_ts(d_tmem, a_addr + kBlk / 4, desc_hi | (b_lo + 2), idesc, 1u);
+          umma_ts(d_tmem, a_addr + kBlk / 4, desc_hi | (b_lo + slab), idesc, 1u);
           accumulate = 1u;
         }
       }
@@ -520,6 +549,27 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     // it, meet at the set's named barrier, and one thread issues the tile's TMA store while the set
     // goes on to its next tile.
     const int n_acc = nb_end - nb0, n_tiles = (n_acc + 1) / 2;
+    if (p.out_t) {
+      // Transposed store (sdd as B A^T): the thread's row is a column of C, so the 32 lanes of a warp write 64
+      // contiguous bytes of one row of C per accumulator column, straight from registers.
+      if (acc_ok) {
+        T* C = static_cast<T*>(p.C);
+        const float bt = p.bias ? to_float(static_cast<const T*>(p.bias)[(long long)batch * p.M + m0 + row]) : 0.f;
+        for (int l = conv_set; l < n_acc; l += kConvSets) {
+          uint32_t r[32];
+          if ((written >> l) & 1u) {
+            tmem_ld_x32(tmem_base + lane_addr + l * kBlk, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0;
+          }
+          T* out = C + ((long long)batch * p.N + (long long)(nb0 + l) * kBlk) * p.M + m0 + row;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) out[(long long)j * p.M] = from_float<T>(__uint_as_float(r[j]) + bt);
+        }
+      }
+    } else
     for (int t = conv_set; t < n_tiles; t += kConvSets) {
       if (acc_ok) {
 #pragma unroll
@@ -562,7 +612,7 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       if (quad == 0 && lane == 0 && acc_ok)
         tma_store_2d(&tm_c, x_ring + t * kSubBytes, (nb0 + 2 * t) * kBlk, batch * p.M + m0);
     }
-    if (quad == 0 && lane == 0) tma_store_commit_and_wait();  // shared memory must outlive the stores' reads
+    if (quad == 0 && lane == 0 && !p.out_t) tma_store_commit_and_wait();  // shared memory must outlive the stores' reads
   }
   tc_fence_before_sync();
   sync_and_drain(failed);
@@ -572,37 +622,53 @@ bsmm_dsd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   }
 }
 
+// The product in this kernel's own terms: C[M, N] (or its transpose) = X[M, K] . W^T, W block-sparse along N.
+struct DsdView {
+  const void* X;
+  const void* W;
+  int M, N, K;
+  int b_mn, out_t;
+};
+
+DsdView dsd_view(const BsmmParams& p) {
+  if (p.mode == MODE_DSD) return {p.A, p.B, p.M, p.N, p.K, p.trans_b ? 0 : 1, 0};
+  return {p.B, p.A, p.N, p.M, p.K, p.trans_a ? 1 : 0, 1};  // sdd: C^T = B A^T
+}
+
 template <int FMT, int NP, bool DEEP_X>
-int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
+int launch_dsd_tc(const BsmmParams& p, const DsdView& v, cudaStream_t st) {
   CUtensorMap tm_x, tm_w;
   {
-    const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.batch * p.M};
-    const uint64_t strides[1] = {(uint64_t)p.K * 2};
+    const uint64_t dims[2] = {(uint64_t)v.K, (uint64_t)p.batch * v.M};
+    const uint64_t strides[1] = {(uint64_t)v.K * 2};
     const uint32_t box[2] = {kSubK, kTileM};
-    int rc = make_tensor_map(&tm_x, p.A, p.dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    int rc = make_tensor_map(&tm_x, v.X, p.dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != SPARTA_OK) return rc;
   }
   {
     const uint64_t dims[2] = {kBlk, (uint64_t)p.batch * p.val_stride_blocks * kBlk};
     const uint64_t strides[1] = {kBlk * 2};
     const uint32_t box[2] = {kBlk, kBlk};
-    int rc = make_tensor_map(&tm_w, p.B, p.dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+    int rc = make_tensor_map(&tm_w, v.W, p.dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc != SPARTA_OK) return rc;
   }
-  CUtensorMap tm_c;
+  CUtensorMap tm_c;  // unused by the transposed store, which writes from registers
   {
-    const uint64_t dims[2] = {(uint64_t)p.N, (uint64_t)p.batch * p.M};
-    const uint64_t strides[1] = {(uint64_t)p.N * 2};
+    const uint64_t dims[2] = {(uint64_t)(v.out_t ? v.M : v.N), (uint64_t)p.batch * (v.out_t ? v.N : v.M)};
+    const uint64_t strides[1] = {dims[0] * 2};
     const uint32_t box[2] = {kSubK, kTileM};
     int rc = make_tensor_map(&tm_c, p.C, p.dtype, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != SPARTA_OK) return rc;
   }
   DsdTcParams q;
   q.row_ptr = p.ptr;
-  q.idx = static_cast<const int32_t*>(p.idx);
+  q.idx = p.idx;
+  q.idx64 = p.idx_is_64;
+  q.b_mn = v.b_mn;
+  q.out_t = v.out_t;
   q.bias = p.bias;
   q.C = p.C;
-  q.M = p.M; q.N = p.N; q.Kb = p.K / kBlk; q.Nb = p.N / kBlk;
+  q.M = v.M; q.N = v.N; q.Kb = v.K / kBlk; q.Nb = v.N / kBlk;
   q.val_stride_blocks = p.val_stride_blocks;
   q.status = device_status_ptr();
   if (!q.status) return SPARTA_ERR_DRIVER;
@@ -610,7 +676,7 @@ int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
   constexpr int kSmemTotal = Lay<NP, DEEP_X>::kSmemTotal;
   static SmemAttrOnce attr;
   if (cudaError_t e = attr.ensure(kern, kSmemTotal); e != cudaSuccess) return static_cast<int>(e);
-  dim3 grid((q.Nb + NP - 1) / NP, p.M / kTileM, p.batch);
+  dim3 grid((q.Nb + NP - 1) / NP, v.M / kTileM, p.batch);
   kern<<<grid, kThreads, kSmemTotal, st>>>(tm_x, tm_w, tm_c, q);
   return launch_status();
 }
@@ -619,13 +685,25 @@ int launch_dsd_tc(const BsmmParams& p, cudaStream_t st) {
 bool bsmm_tc_available() { return true; }
 
 bool dsd_tc_supported(const BsmmParams& p) {
-  if (p.mode != MODE_DSD || !p.trans_b || p.trans_a || !p.compressed || p.idx_is_64) return false;
+  // dsd with either weight layout (BCSR [N, K]; BCSC [K, N], 32-bit or with the BCSR value position), and sdd
+  // against a dense B stored [N, K]; the dense operand must have the reduction dimension contiguous
+  if (p.mode == MODE_DSD) {
+    if (p.trans_a || p.BM != kTileM || p.BN != kBlk) return false;
+    if (p.trans_b && p.idx_is_64) return false;  // 64-bit entries exist in the BCSC order only
+  } else if (p.mode == MODE_SDD) {
+    if (!p.trans_b || p.BM != kBlk || p.BN != kTileM) return false;
+    if (!p.trans_a && p.idx_is_64) return false;
+  } else {
+    return false;
+  }
+  if (!p.compressed || p.BK != kBlk) return false;
   if (p.dtype != SPARTA_F16 && p.dtype != SPARTA_BF16) return false;
-  if (p.BM != kTileM || p.BK != kBlk || p.BN != kBlk) return false;
-  if (p.M % kTileM || p.K % kBlk || p.N % kBlk) return false;
-  if (p.K / kBlk > kMaxKb || p.n_index_sets != 1 || p.val_stride_blocks <= 0) return false;
+  const DsdView v = dsd_view(p);
+  if (v.M % kTileM || v.K % kBlk || v.N % kBlk) return false;
+  if (v.K / kBlk > kMaxKb || v.N / kBlk > 0xffff || p.n_index_sets != 1 || p.val_stride_blocks <= 0) return false;
   if ((long long)p.batch * p.val_stride_blocks * kBlk > 0x7fffffffll) return false;
-  if ((long long)p.batch * p.M > 0x7fffffffll || p.batch > 65535 || p.M / kTileM > 65535) return false;
+  if ((long long)p.batch * v.M > 0x7fffffffll || (long long)p.batch * v.N > 0x7fffffffll) return false;
+  if (p.batch > 65535 || v.M / kTileM > 65535) return false;
   if (!aligned(p.A, 16) || !aligned(p.B, 16) || !aligned(p.C, 16)) return false;
   return true;
 }
@@ -635,26 +713,27 @@ int dsd_tc_launch(const BsmmParams& p, cudaStream_t st) {
   // CTAs, wider ones re-read the activations less.  Cost model: waves of CTAs x (a fixed part per CTA
   // + the panel's share of the blocks), fitted to the 4096^3 measurements (10 columns beat 12 by 4 %, 8
   // lost 17 %).
-  const long long tiles = (long long)(p.M / kTileM) * p.batch;
+  const DsdView v = dsd_view(p);
+  const long long tiles = (long long)(v.M / kTileM) * p.batch;
   int best = 12;
   long long best_cost = -1;
   for (int np : {12, 10, 8}) {
-    const long long ctas = (long long)((p.N / kBlk + np - 1) / np) * tiles;
+    const long long ctas = (long long)((v.N / kBlk + np - 1) / np) * tiles;
     const long long cost = ((ctas + kNumSMs - 1) / kNumSMs) * (6 + np);
     if (best_cost < 0 || cost < best_cost) { best = np; best_cost = cost; }
   }
   // sparse masks (few W blocks per step) take the variant with a fourth X slot, see x_slots()
-  const double density = (double)p.val_stride_blocks / ((double)(p.N / kBlk) * (double)(p.K / kBlk));
+  const double density = (double)p.val_stride_blocks / ((double)(v.N / kBlk) * (double)(v.K / kBlk));
   const bool deep_x = best <= 10 && density <= 0.15;
   const bool h = p.dtype == SPARTA_F16;
   switch (best) {
     case 8:
-      if (deep_x) return h ? launch_dsd_tc<0, 8, true>(p, st) : launch_dsd_tc<1, 8, true>(p, st);
-      return h ? launch_dsd_tc<0, 8, false>(p, st) : launch_dsd_tc<1, 8, false>(p, st);
+      if (deep_x) return h ? launch_dsd_tc<0, 8, true>(p, v, st) : launch_dsd_tc<1, 8, true>(p, v, st);
+      return h ? launch_dsd_tc<0, 8, false>(p, v, st) : launch_dsd_tc<1, 8, false>(p, v, st);
     case 10:
-      if (deep_x) return h ? launch_dsd_tc<0, 10, true>(p, st) : launch_dsd_tc<1, 10, true>(p, st);
-      return h ? launch_dsd_tc<0, 10, false>(p, st) : launch_dsd_tc<1, 10, false>(p, st);
-    default: return h ? launch_dsd_tc<0, 12, false>(p, st) : launch_dsd_tc<1, 12, false>(p, st);
+      if (deep_x) return h ? launch_dsd_tc<0, 10, true>(p, v, st) : launch_dsd_tc<1, 10, true>(p, v, st);
+      return h ? launch_dsd_tc<0, 10, false>(p, v, st) : launch_dsd_tc<1, 10, false>(p, v, st);
+    default: return h ? launch_dsd_tc<0, 12, false>(p, v, st) : launch_dsd_tc<1, 12, false>(p, v, st);
   }
 }
 

@@ -1,4 +1,6 @@
 // Host-side support of the tcgen05 kernels: tensor-map encoding and the device status words.
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "tc_common.cuh"
@@ -43,14 +45,29 @@ int make_tensor_map(CUtensorMap* map, const void* base, int dtype, int rank, con
       if (s[i] % 16) return SPARTA_ERR_ALIGN;
     }
   }
-  CUresult r = fn(map, dt, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  auto encode = [&] {
+    return fn(map, dt, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode();
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // A thread that has made no runtime call yet that needs the device (an autograd worker thread running a
+    // backward kernel) has no driver context bound; the runtime binds the primary one on such a call.
+    cudaFree(nullptr);
+    r = encode();
+  }
+  if (r != CUDA_SUCCESS && std::getenv("SPARTA_B200_DEBUG"))
+    std::fprintf(stderr, "sparta_b200: cuTensorMapEncodeTiled -> %d (base %p, rank %d, dims %llu x %llu, pitch %llu, box %u x %u)\n",
+                 (int)r, base, rank, (unsigned long long)d[0], (unsigned long long)d[1], (unsigned long long)s[0], b[0], b[1]);
   return r == CUDA_SUCCESS ? SPARTA_OK : SPARTA_ERR_DRIVER;
 }
 
 int32_t* device_status_ptr() {
   void* p = nullptr;
-  if (cudaGetSymbolAddress(&p, g_status) != cudaSuccess) return nullptr;
+  if (cudaError_t e = cudaGetSymbolAddress(&p, g_status); e != cudaSuccess) {
+    if (std::getenv("SPARTA_B200_DEBUG")) std::fprintf(stderr, "sparta_b200: cudaGetSymbolAddress -> %d\n", (int)e);
+    return nullptr;
+  }
   return static_cast<int32_t*>(p);
 }
 

@@ -125,9 +125,16 @@ def test_search_space_follows_the_tile_table():
     kernel._check_parameters({f'BLOCK_SIZE_{d}_VALUE': v for d, v in zip('MKN', (64, 16, 32))})
     with pytest.raises(AssertionError):
         kernel._check_parameters({f'BLOCK_SIZE_{d}_VALUE': v for d, v in zip('MKN', (128, 64, 32))})
-    # the backward:A kernel of that operator is dsd with B stored [K, N]: no tcgen05 tile
+    # the two gradients of that operator have tcgen05 tiles too: dsd with B stored [K, N], dds with A stored [K, M]
     bwd = op.get_kernel_placeholders(True)['backward:A'].possible_kernels['sparta']
-    assert all(impl == _lib.IMPL_SIMT for impl in bwd.tile_shapes(torch.float16).values())
+    assert bwd.tile_shapes(torch.float16)[(128, 32, 32)] == _lib.IMPL_TCGEN05
+    bwd = op.get_kernel_placeholders(True)['backward:B'].possible_kernels['sparta']
+    assert bwd.tile_shapes(torch.float16)[(32, 64, 32)] == _lib.IMPL_TCGEN05
+    # sdd: only against a dense B stored [N, K]
+    from sparta_b200.specializer.kernels import SparTASparseMatMulKernel
+    sdd = lambda tb: SparTASparseMatMulKernel(mode='sdd', biased=False, transpose_A=False, transpose_B=tb)
+    assert sdd(True).tile_shapes(torch.float16)[(32, 32, 128)] == _lib.IMPL_TCGEN05
+    assert all(impl == _lib.IMPL_SIMT for impl in sdd(False).tile_shapes(torch.float16).values())
 
 
 def test_grid_and_random_walkers():

@@ -149,3 +149,152 @@ def test_tune_reaches_the_tcgen05_kernel():
     pinned = {'forward:C': {**cfg, '_family': 'tcgen05'}}
     sparse_linear.build(pinned, sample_inputs=[x])
     assert torch.equal(sparse_linear(x), y)
+
+
+def _run_both_families(kernel, cfg, simt_cfg, args):
+    kernel.compile({**cfg, '_family': 'tcgen05'})
+    out = kernel(*args)
+    assert _lib.last_status() == [0, 0, 0, 0]
+    kernel.compile({**simt_cfg, '_family': 'simt'})
+    return out, kernel(*args)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('both_forms', [False, True])  # BCSC alone (values in BCSC order), or 64-bit entries into BCSR order
+@pytest.mark.parametrize('batch,M,K,N,sparsity', [
+    (1, 128, 64, 32, 0.0),
+    (2, 256, 256, 192, 0.5),
+    (1, 512, 1024, 1024, 0.9),
+    (1, 384, 2048, 544, 0.75),
+    (1, 128, 96, 416, 0.5),
+    (2, 256, 4096, 384, 0.97),
+])
+def test_dsd_nn_tcgen05(dtype, both_forms, batch, M, K, N, sparsity):
+    """The SparseLinear input gradient: B stored [K, N] and indexed by column (BCSC), blocks MN-major."""
+    g = torch.Generator().manual_seed(M + K + N + 1)
+    x = torch.randn((batch, M, K), generator=g).to(dtype)
+    w = (torch.randn((batch, K, N), generator=g) * 0.1).to(dtype)
+    mask = oracle.block_mask((K, N), (32, 32), sparsity, generator=g)
+    if N >= 192:
+        mask[:, 32:64] = 0  # a block column without any block
+    w = w * mask
+    kernel = SparTASparseMatMulKernel(mode='dsd', biased=False, transpose_A=False, transpose_B=False,
+                                      compressed=True)
+    if both_forms:
+        kernel.ports['B'].set_sparse(True, True)
+    kernel.ports['B'].set_mask(mask.cuda())
+    kernel.set_shape(batch, M, K, N)
+    cfg = {'_impl': 'sparta', 'BLOCK_SIZE_K_VALUE': 32, 'BLOCK_SIZE_N_VALUE': 32}
+    kernel.compile({**cfg, 'BLOCK_SIZE_M_VALUE': 128, '_family': 'tcgen05'})
+    ix = kernel.ports['B'].indexes
+    args = [x.cuda(), ix.convert(w.cuda())]
+    out, ref = _run_both_families(kernel, {**cfg, 'BLOCK_SIZE_M_VALUE': 128}, {**cfg, 'BLOCK_SIZE_M_VALUE': 64}, args)
+    expect = oracle.matmul_reference(x.float(), w.float(), None, mask, 'dsd', False, False, (32, 32))
+    torch.testing.assert_close(out.float().cpu(), expect, **TOL)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('trans_A,both_forms', [(False, False), (True, False), (True, True)])
+@pytest.mark.parametrize('batch,M,K,N,sparsity,biased', [
+    (1, 32, 64, 128, 0.0, False),
+    (2, 192, 256, 256, 0.5, True),
+    (1, 1024, 1024, 512, 0.9, False),
+    (1, 544, 2048, 384, 0.75, True),
+    (2, 384, 4096, 256, 0.97, True),
+])
+def test_sdd_tcgen05(dtype, trans_A, both_forms, batch, M, K, N, sparsity, biased):
+    """sdd against a dense B stored [N, K] runs as C^T = B A^T on the dsd kernel with a transposed store."""
+    g = torch.Generator().manual_seed(M + K + N + 2)
+    a = (torch.randn((batch, K, M) if trans_A else (batch, M, K), generator=g) * 0.1).to(dtype)
+    b = torch.randn((batch, N, K), generator=g).to(dtype)
+    bias = torch.randn((batch, N), generator=g).to(dtype) if biased else None
+    mask = oracle.block_mask((K, M) if trans_A else (M, K), (32, 32), sparsity, generator=g)
+    if M >= 192:
+        if trans_A:
+            mask[:, 32:64] = 0
+        else:
+            mask[32:64] = 0  # a block row of A without any block: those rows of C are bias only
+    a = a * mask
+    kernel = SparTASparseMatMulKernel(mode='sdd', biased=biased, transpose_A=trans_A, transpose_B=True,
+                                      compressed=True)
+    if both_forms:
+        kernel.ports['A'].set_sparse(True, True)
+    kernel.ports['A'].set_mask(mask.cuda())
+    kernel.set_shape(batch, M, K, N)
+    cfg = {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': 32, 'BLOCK_SIZE_K_VALUE': 32}
+    kernel.compile({**cfg, 'BLOCK_SIZE_N_VALUE': 128, '_family': 'tcgen05'})
+    ix = kernel.ports['A'].indexes
+    args = [ix.convert(a.cuda()), b.cuda()] + ([bias.cuda()] if biased else [])
+    out, ref = _run_both_families(kernel, {**cfg, 'BLOCK_SIZE_N_VALUE': 128}, {**cfg, 'BLOCK_SIZE_N_VALUE': 64}, args)
+    expect = oracle.matmul_reference(a.float(), b.float(), bias.float() if biased else None, mask, 'sdd',
+                                     trans_A, True, (32, 32))
+    torch.testing.assert_close(out.float().cpu(), expect, **TOL)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('trans_B', [True, False])
+@pytest.mark.parametrize('compressed', [True, False])
+@pytest.mark.parametrize('batch,M,K,N,sparsity', [
+    (1, 128, 64, 32, 0.0),
+    (2, 256, 256, 320, 0.5),
+    (1, 512, 1024, 1024, 0.9),
+    (1, 384, 128, 2048, 0.97),
+])
+def test_dds_tn_tcgen05(dtype, trans_B, compressed, batch, M, K, N, sparsity):
+    """The SparseLinear weight gradient: A stored [K, M] (MN-major A operand)."""
+    g = torch.Generator().manual_seed(M + K + N + 3)
+    A = torch.randn((batch, K, M), generator=g).to(dtype)
+    B = (torch.randn((batch, N, K) if trans_B else (batch, K, N), generator=g) * 0.1).to(dtype)
+    mask = oracle.block_mask((M, N), (32, 32), sparsity, generator=g)
+    kernel = SparTASparseMatMulKernel(mode='dds', biased=False, transpose_A=True, transpose_B=trans_B,
+                                      compressed=compressed)
+    kernel.ports['C'].set_mask(mask.cuda())
+    kernel.set_shape(batch, M, K, N)
+    cfg = {'_impl': 'sparta', 'BLOCK_SIZE_M_VALUE': 32, 'BLOCK_SIZE_K_VALUE': 64, 'BLOCK_SIZE_N_VALUE': 32}
+    kernel.compile({**cfg, '_family': 'tcgen05'})
+    ix = kernel.ports['C'].indexes
+    out, ref = _run_both_families(kernel, cfg, cfg, [A.cuda(), B.cuda()])
+    dense = ix.inverse(out) if compressed else out
+    expect = oracle.matmul_reference(A.float(), B.float(), None, mask, 'dds', True, trans_B, (32, 32))
+    torch.testing.assert_close(dense.float().cpu(), expect, **TOL)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_sparse_linear_trains_on_tcgen05(dtype):
+    """Forward, input gradient and weight gradient of SparseLinear all on the tcgen05 kernels, against
+    the oracle's autograd on the masked dense layer."""
+    from sparta_b200.nn import SparseLinear
+    M, K, N = 512, 768, 640
+    g = torch.Generator().manual_seed(11)
+    mask = oracle.block_mask((N, K), (32, 32), 0.8, generator=g)
+    dense = torch.nn.Linear(K, N, dtype=dtype)
+    with torch.no_grad():
+        dense.weight.copy_((torch.randn((N, K), generator=g) * 0.05).to(dtype))
+        dense.bias.copy_(torch.randn((N,), generator=g).to(dtype))
+    x = torch.randn((M, K), generator=g).to(dtype)
+    gy = (torch.randn((M, N), generator=g) * 0.1).to(dtype)
+    op = SparseLinear(dense.cuda(), weight_mask=mask.cuda())
+    tc = {'_impl': 'sparta', '_family': 'tcgen05'}
+    op.build({
+        'forward:C': {**tc, 'BLOCK_SIZE_M_VALUE': 128, 'BLOCK_SIZE_K_VALUE': 32, 'BLOCK_SIZE_N_VALUE': 32},
+        'backward:A': {**tc, 'BLOCK_SIZE_M_VALUE': 128, 'BLOCK_SIZE_K_VALUE': 32, 'BLOCK_SIZE_N_VALUE': 32},
+        'backward:B': {**tc, 'BLOCK_SIZE_M_VALUE': 32, 'BLOCK_SIZE_K_VALUE': 64, 'BLOCK_SIZE_N_VALUE': 32},
+    }, sample_inputs=[x.cuda()])
+    xg = x.cuda().requires_grad_(True)
+    y = op(xg)
+    y.backward(gy.cuda())
+    assert _lib.last_status() == [0, 0, 0, 0]
+    # oracle: fp32 autograd on the masked dense layer
+    xr = x.float().requires_grad_(True)
+    wr = (dense.weight.detach().float().cpu() * mask).requires_grad_(True)
+    br = dense.bias.detach().float().cpu().requires_grad_(True)
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(gy.float())
+    torch.testing.assert_close(y.float().cpu(), yr.detach(), **TOL)
+    torch.testing.assert_close(xg.grad.float().cpu(), xr.grad, **TOL)
+    gw = op.get_sparse_indexes('B').inverse(op.weight.grad.unsqueeze(0)).squeeze(0)  # the weight is held compressed
+    torch.testing.assert_close(gw.float().cpu(), wr.grad * mask, rtol=2e-2, atol=5e-2)
+    torch.testing.assert_close(op.bias.grad.float().cpu(), br.grad, rtol=2e-2, atol=1e-1)
