@@ -544,7 +544,7 @@ def run_extras(device, peaks, flush, only=None):
         extras['refgrid'] = refgrid_extras(device, timed)
     except Exception as e:
         extras['refgrid'] = {'error': repr(e)[:200]}
-    return {k: v for k, v in extras.items() if 'skipped' not in str(v.get('error', ''))}
+    return {k: v for k, v in extras.items() if not (isinstance(v, dict) and 'skipped' in str(v.get('error', '')))}
 
 
 

@@ -45,13 +45,13 @@ struct DdsTcParams {
   const void* bias;
   void* C;
   int M, N, K, Nb;
-  int compressed, trans_a, trans_b;
+  int compressed, trans_b;
   int n_index_sets;
   long long ptr_stride, idx_stride, val_stride_blocks;
   int32_t* status;
 };
 
-template <int FMT, int STAGES, bool LOOP>
+template <int FMT, int STAGES, bool LOOP, bool TA>
 __global__ void __launch_bounds__(kThreads, STAGES == 2 ? 2 : 1)
 bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    DdsTcParams p) {
@@ -143,12 +143,13 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       uint8_t* st = stages + s * kStageBytes;
       if (lane == 0) {
         mbar_arrive_expect_tx(&full_bar[s], kABytes + ncols * kBBlockBytes);
-        if (!p.trans_a) tma_load_2d(st, &tm_a, c * kChunkK, batch * p.M + tile * kTileM, &full_bar[s]);
+        if constexpr (!TA) tma_load_2d(st, &tm_a, c * kChunkK, batch * p.M + tile * kTileM, &full_bar[s]);
       }
-      __syncwarp();  // the expected byte count is registered before any lane's load can complete
-      if (p.trans_a && lane >= 16 && lane < 20)  // A stored [K, M]: the tile's four block rows, 32 rows contiguous per K row
-        tma_load_2d(st + (lane - 16) * kBBlockBytes, &tm_a, tile * kTileM + (lane - 16) * kBlk, batch * p.K + c * kChunkK,
-                    &full_bar[s]);
+      if constexpr (TA) {  // A stored [K, M]: the tile's four block rows, 32 rows contiguous per K row
+        if (lane >= 16 && lane < 20)
+          tma_load_2d(st + (lane - 16) * kBBlockBytes, &tm_a, tile * kTileM + (lane - 16) * kBlk, batch * p.K + c * kChunkK,
+                      &full_bar[s]);
+      }
       if (lane < ncols) {
         uint8_t* dst = st + kABytes + lane * kBBlockBytes;
         if (p.trans_b) tma_load_2d(dst, &tm_b, c * kChunkK, batch * p.N + col * kBlk, &full_bar[s]);
@@ -162,12 +163,12 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     // A: K-major, 128-byte swizzle.  B: K-major 128-byte swizzle when stored [N, K]; MN-major 64-byte
     // swizzle when stored [K, N] (32 columns contiguous per K row, column blocks 4 KB apart).
     // A stored [K, M] is the mirror of B stored [K, N]: MN-major, block rows 4 KB apart.
-    const uint64_t a_hi = p.trans_a ? make_smem_desc(0, kBBlockBytes, 512, SW_64B) : make_smem_desc(0, 16, 1024, SW_128B);
-    const uint32_t a_step = p.trans_a ? (16u * 64u) >> 4 : 2u;
+    const uint64_t a_hi = TA ? make_smem_desc(0, kBBlockBytes, 512, SW_64B) : make_smem_desc(0, 16, 1024, SW_128B);
+    constexpr uint32_t a_step = TA ? (16u * 64u) >> 4 : 2u;
     const uint64_t b_hi = p.trans_b ? make_smem_desc(0, 16, 1024, SW_128B)
                                     : make_smem_desc(0, kBBlockBytes, 512, SW_64B);
     const uint32_t b_step = p.trans_b ? 2u : (16u * 64u) >> 4;  // 16 K elements, in 16-byte units
-    const uint32_t idesc = make_idesc_f16(kTileM, kBlk * ncols, FMT, p.trans_a ? 1 : 0, p.trans_b ? 0 : 1);
+    const uint32_t idesc = make_idesc_f16(kTileM, kBlk * ncols, FMT, TA ? 1 : 0, p.trans_b ? 0 : 1);
     const uint32_t base = smem_u32(stages) >> 4;
     bool ok = true;
     for (int c = 0; c < nchunks; ++c) {
@@ -256,10 +257,10 @@ bsmm_dds_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   }
 }
 
-template <int FMT, int STAGES>
+template <int FMT, int STAGES, bool TA>
 int launch_dds(const BsmmParams& p, cudaStream_t st) {
   CUtensorMap tm_a, tm_b;
-  if (p.trans_a) {
+  if (TA) {
     const uint64_t dims[2] = {(uint64_t)p.M, (uint64_t)p.batch * p.K};
     const uint64_t strides[1] = {(uint64_t)p.M * 2};
     const uint32_t box[2] = {kBlk, kChunkK};
@@ -291,16 +292,16 @@ int launch_dds(const BsmmParams& p, cudaStream_t st) {
   q.bias = p.bias;
   q.C = p.C;
   q.M = p.M; q.N = p.N; q.K = p.K; q.Nb = p.N / kBlk;
-  q.compressed = p.compressed; q.trans_a = p.trans_a; q.trans_b = p.trans_b;
+  q.compressed = p.compressed; q.trans_b = p.trans_b;
   q.n_index_sets = p.n_index_sets;
   q.ptr_stride = p.ptr_stride; q.idx_stride = p.idx_stride; q.val_stride_blocks = p.val_stride_blocks;
   q.status = device_status_ptr();
   if (!q.status) return SPARTA_ERR_DRIVER;
   constexpr int kSmem = smem_bytes(STAGES);
   static SmemAttrOnce attr_one, attr_loop;
-  if (cudaError_t e = attr_one.ensure(bsmm_dds_tc_kernel<FMT, STAGES, false>, kSmem); e != cudaSuccess)
+  if (cudaError_t e = attr_one.ensure(bsmm_dds_tc_kernel<FMT, STAGES, false, TA>, kSmem); e != cudaSuccess)
     return static_cast<int>(e);
-  if (cudaError_t e = attr_loop.ensure(bsmm_dds_tc_kernel<FMT, STAGES, true>, kSmem); e != cudaSuccess)
+  if (cudaError_t e = attr_loop.ensure(bsmm_dds_tc_kernel<FMT, STAGES, true, TA>, kSmem); e != cudaSuccess)
     return static_cast<int>(e);
   // CTAs per row tile: every group its own CTA when there are few row tiles; with many (batched masks)
   // most groups of a tile are empty, and a few CTAs per tile loop over the groups instead, aiming at
@@ -312,10 +313,10 @@ int launch_dds(const BsmmParams& p, cudaStream_t st) {
   if (per_tile < 1) per_tile = 1;
   if (per_tile >= n_groups) {
     dim3 grid(n_groups, p.M / kTileM, p.batch);
-    bsmm_dds_tc_kernel<FMT, STAGES, false><<<grid, kThreads, kSmem, st>>>(tm_a, tm_b, q);
+    bsmm_dds_tc_kernel<FMT, STAGES, false, TA><<<grid, kThreads, kSmem, st>>>(tm_a, tm_b, q);
   } else {
     dim3 grid((unsigned)per_tile, p.M / kTileM, p.batch);
-    bsmm_dds_tc_kernel<FMT, STAGES, true><<<grid, kThreads, kSmem, st>>>(tm_a, tm_b, q);
+    bsmm_dds_tc_kernel<FMT, STAGES, true, TA><<<grid, kThreads, kSmem, st>>>(tm_a, tm_b, q);
   }
   return launch_status();
 }
@@ -336,8 +337,13 @@ bool dds_tc_supported(const BsmmParams& p) {
 }
 
 int dds_tc_launch(const BsmmParams& p, cudaStream_t st) {
-  if (p.K <= 2 * kChunkK) return p.dtype == SPARTA_F16 ? launch_dds<0, 2>(p, st) : launch_dds<1, 2>(p, st);
-  return p.dtype == SPARTA_F16 ? launch_dds<0, 4>(p, st) : launch_dds<1, 4>(p, st);
+  const bool h = p.dtype == SPARTA_F16;
+  if (p.K <= 2 * kChunkK) {
+    if (p.trans_a) return h ? launch_dds<0, 2, true>(p, st) : launch_dds<1, 2, true>(p, st);
+    return h ? launch_dds<0, 2, false>(p, st) : launch_dds<1, 2, false>(p, st);
+  }
+  if (p.trans_a) return h ? launch_dds<0, 4, true>(p, st) : launch_dds<1, 4, true>(p, st);
+  return h ? launch_dds<0, 4, false>(p, st) : launch_dds<1, 4, false>(p, st);
 }
 
 }  // namespace sparta
