@@ -112,6 +112,10 @@ template <> struct Pair<__nv_bfloat16> {
 };
 
 template <typename T>
+__device__ __forceinline__ void softmax_row_in_registers(const SmParams& p, uint4 (&raw)[kVecs], const uint32_t (&off)[kVecs],
+                                                         int n, int lane, T* out);
+
+template <typename T>
 __global__ void __launch_bounds__(128, 9) softmax_fwd_vec_kernel(SmParams p) {
   constexpr int E = 16 / sizeof(T);
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -146,7 +150,6 @@ __global__ void __launch_bounds__(128, 9) softmax_fwd_vec_kernel(SmParams p) {
     }
     return;
   }
-  const float scale2 = p.scale * 1.4426950408889634f;
   uint32_t off[kVecs];  // within one batch slice (the host checks that a slice has fewer than 2^32 elements)
   uint4 raw[kVecs];  // the row's values stay packed in their own type: 32 registers, so four CTAs fit an SM
 #pragma unroll
@@ -157,6 +160,16 @@ __global__ void __launch_bounds__(128, 9) softmax_fwd_vec_kernel(SmParams p) {
       raw[i] = *reinterpret_cast<const uint4*>(x + off[i]);
     }
   }
+  softmax_row_in_registers<T>(p, raw, off, n, lane, out);
+}
+
+// The row's values are in raw[] (vector i of a lane = elements (lane + 32 i) E .. + E - 1 of the kept row, at
+// element offset off[i] of the tensors): maximum, probabilities, sum, normalise, store.
+template <typename T>
+__device__ __forceinline__ void softmax_row_in_registers(const SmParams& p, uint4 (&raw)[kVecs], const uint32_t (&off)[kVecs],
+                                                         int n, int lane, T* out) {
+  constexpr int E = 16 / sizeof(T);
+  const float scale2 = p.scale * 1.4426950408889634f;
   // pass 1: maximum; masked elements become -inf in place, so the later passes need no mask
   float m = -INFINITY;
 #pragma unroll
@@ -241,6 +254,202 @@ __global__ void __launch_bounds__(128, 9) softmax_fwd_vec_kernel(SmParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Forward pass with the loads staged through shared memory.  In the kernel above a row's loads occupy the
+// registers that later hold the row, so a warp alternates between waiting for its loads and storing, and
+// the bytes an SM keeps in flight are bounded by its register file.  Here a warp owns up to kRingRows
+// rows of one block row (every kRingWarps-th row of its CTA's share) and a private ring in shared memory; it issues the asynchronous copies
+// (cp.async, 16 bytes per lane) of the rows up to `slots - 1` ahead of the one it computes, so about
+// 150 KB per SM are in flight whatever the warps are doing.  A lane copies, reads back and stores the
+// same 16-byte vectors, so the ring needs no barrier: its own wait_group orders the copy before the read,
+// and the read's register dependency orders it before the slot is refilled.  The offsets of a row are
+// those of the warp's first row plus a row step.  Used when block rows have at least 16 rows.
+// ---------------------------------------------------------------------------------------------------
+constexpr int kRingRows = 16;            // rows per warp at most; a CTA takes kRingWarps x rows consecutive rows of a block row
+constexpr int kRingBytes = 12 * 1024;    // ring capacity per warp
+constexpr int kRingWarps = 4;            // warps per CTA: 48 KB of shared memory, four CTAs per SM
+constexpr int kRingMaxSlots = 8;
+
+__device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gptr) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gptr) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// at most `pending` of this thread's copy groups may still be in flight
+__device__ __forceinline__ void cp_async_wait_pending(int pending) {
+  switch (pending) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+  }
+}
+
+// Softmax of one row that sits in shared memory as nv 16-byte vectors (vector v = elements v E .. of the kept
+// row, at element offset off_of(v) of the tensors); every lane touches only its own vectors.
+template <typename T, typename OffsetOf>
+__device__ __forceinline__ void softmax_row_in_shared(const SmParams& p, uint8_t* slot, int nv, int lane, T* out,
+                                                      OffsetOf off_of) {
+  constexpr int E = 16 / sizeof(T);
+  const float scale2 = p.scale * 1.4426950408889634f;
+  uint4* vecs = reinterpret_cast<uint4*>(slot);
+  float m = -INFINITY;
+  for (int v = lane; v < nv; v += 32) {
+    uint4 raw = vecs[v];
+    T* e = reinterpret_cast<T*>(&raw);
+    if (p.mask) {
+      const uint32_t o = off_of(v);
+      unsigned long long mk;
+      if (E == 8) mk = *reinterpret_cast<const unsigned long long*>(p.mask + o);
+      else mk = *reinterpret_cast<const unsigned int*>(p.mask + o);
+#pragma unroll
+      for (int k = 0; k < E; ++k)
+        if (!((mk >> (8 * k)) & 0xffull)) e[k] = from_float<T>(-INFINITY);
+      vecs[v] = raw;
+    }
+#pragma unroll
+    for (int k = 0; k < E; ++k) m = fmaxf(m, to_float(e[k]));
+  }
+  const float mw = warp_max(m) * scale2;
+  const float sub = mw > -INFINITY ? mw : 0.f;
+  float sum = 0.f;
+  for (int v = lane; v < nv; v += 32) {
+    uint4 raw = vecs[v];
+    T* e = reinterpret_cast<T*>(&raw);
+    float pe[E];
+#pragma unroll
+    for (int k = 0; k < E; ++k) {
+      pe[k] = ex2_approx(fmaf(to_float(e[k]), scale2, -sub));
+      sum += pe[k];
+    }
+    // the unnormalised probabilities go back into the slot in the row's own type, as in the register path
+#pragma unroll
+    for (int k = 0; k < E; ++k) e[k] = from_float<T>(pe[k]);
+    vecs[v] = raw;
+  }
+  sum = warp_sum(sum);
+  const float inv = sum > 0.f ? 1.f / sum : 0.f;
+  for (int v = lane; v < nv; v += 32) {
+    uint4 raw = vecs[v];
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int k = 0; k < E; ++k) e[k] = from_float<T>(to_float(e[k]) * inv);
+    *reinterpret_cast<uint4*>(out + off_of(v)) = raw;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRingWarps * 32, 4) softmax_fwd_ring_kernel(SmParams p) {
+  constexpr int E = 16 / sizeof(T);
+  extern __shared__ __align__(16) uint8_t ring_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the warps of a CTA interleave: together they read kRingWarps consecutive rows (one contiguous piece of every
+  // block of the block row) at a time, which keeps the DRAM accesses of a CTA next to each other
+  const int rows_w = min(kRingRows, p.BH / kRingWarps);
+  const int row0 = blockIdx.x * kRingWarps * rows_w + warp;
+  if (row0 >= p.H) return;
+  const long long bstride = p.compressed ? p.val_stride_blocks * p.BH * p.BW : (long long)p.H * p.W;
+  const T* x = static_cast<const T*>(p.x) + (long long)blockIdx.y * bstride;
+  T* out = static_cast<T*>(p.out) + (long long)blockIdx.y * bstride;
+  const int br = row0 / p.BH, y0 = row0 - br * p.BH;
+  const int t0 = p.row_ptr[br], t1 = p.row_ptr[br + 1];
+  const int n = (t1 - t0) * p.BW;
+  const int shift = __ffs(p.BW) - 1;
+  const int nv = n / E;
+  if (nv * 16 > kRingBytes) {  // rows too long for the ring: the scalar two-pass path, row by row
+    for (int k = 0; k < rows_w; ++k) {
+      const int row = row0 + k * kRingWarps, y = y0 + k * kRingWarps;
+      float m = -INFINITY, sum = 0.f;
+      for (int j = lane; j < n; j += 32) {
+        const long long o = elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1));
+        if (p.mask && !p.mask[o]) continue;
+        const float v = to_float(x[o]) * p.scale;
+        if (v > m) { sum = sum * expf(m - v) + 1.f; m = v; }
+        else sum += expf(v - m);
+      }
+      const float mw = warp_max(m);
+      sum = (m == -INFINITY) ? 0.f : sum * expf(m - mw);
+      sum = warp_sum(sum);
+      const float inv = sum > 0.f ? 1.f / sum : 0.f;
+      for (int j = lane; j < n; j += 32) {
+        const long long o = elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1));
+        float r = 0.f;
+        if (!p.mask || p.mask[o]) r = expf(to_float(x[o]) * p.scale - mw) * inv;
+        out[o] = from_float<T>(r);
+      }
+    }
+    return;
+  }
+  if (n == 0) return;
+  // offsets of the warp's first row; row k adds k row steps
+  uint32_t off0[kVecs];
+#pragma unroll
+  for (int i = 0; i < kVecs; ++i) {
+    const int j = (lane + 32 * i) * E;
+    off0[i] = j < n ? static_cast<uint32_t>(elem_off(p, t0 + (j >> shift), row0, y0, j & (p.BW - 1))) : 0u;
+  }
+  const uint32_t row_step = (p.compressed ? p.BW : p.W) * kRingWarps;
+  const int row_bytes = nv * 16;  // at most the ring's capacity
+  int slots = kRingBytes / row_bytes;
+  if (slots > kRingMaxSlots) slots = kRingMaxSlots;
+  const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(ring_smem)) + warp * kRingBytes;
+  const uint8_t* ring_ptr = ring_smem + warp * kRingBytes;
+
+  auto issue = [&](int k) {  // copies of row k (none beyond the warp's rows), always one group
+    if (k < rows_w) {
+      const uint32_t dst = ring + (k % slots) * row_bytes;
+#pragma unroll
+      for (int i = 0; i < kVecs; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nv) cp_async_16(dst + v * 16, x + off0[i] + k * row_step);
+      }
+    }
+    cp_async_commit();
+  };
+  if (nv > 32 * kVecs) {
+    // Rows longer than the registers hold (up to the ring's 12 KB) stay in shared memory: the same pipeline,
+    // with the three passes reading and rewriting the row's slot.  A lane owns vectors lane, lane + 32, ...
+    const uint32_t step = p.compressed ? p.BW : p.W;
+    auto vec_off = [&](int v, int k) -> uint32_t {
+      const int j = v * E;
+      return static_cast<uint32_t>(elem_off(p, t0 + (j >> shift), row0, y0, j & (p.BW - 1))) + k * kRingWarps * step;
+    };
+    auto issue_long = [&](int k) {
+      if (k < rows_w) {
+        const uint32_t dst = ring + (k % slots) * row_bytes;
+        for (int v = lane; v < nv; v += 32) cp_async_16(dst + v * 16, x + vec_off(v, k));
+      }
+      cp_async_commit();
+    };
+    for (int k = 0; k < slots - 1; ++k) issue_long(k);
+    for (int k = 0; k < rows_w; ++k) {
+      issue_long(k + slots - 1);
+      cp_async_wait_pending(slots - 1);
+      softmax_row_in_shared<T>(p, const_cast<uint8_t*>(ring_ptr) + (k % slots) * row_bytes, nv, lane, out,
+                               [&](int v) { return vec_off(v, k); });
+    }
+    return;
+  }
+  for (int k = 0; k < slots - 1; ++k) issue(k);
+  for (int k = 0; k < rows_w; ++k) {
+    issue(k + slots - 1);            // into the slot read in the previous iteration
+    cp_async_wait_pending(slots - 1);  // row k has landed
+    const uint8_t* src = ring_ptr + (k % slots) * row_bytes;
+    uint4 raw[kVecs];
+    uint32_t off[kVecs];
+#pragma unroll
+    for (int i = 0; i < kVecs; ++i) {
+      const int v = lane + 32 * i;
+      off[i] = off0[i] + k * row_step;
+      if (v < nv) raw[i] = *reinterpret_cast<const uint4*>(src + v * 16);
+    }
+    softmax_row_in_registers<T>(p, raw, off, n, lane, out);
+  }
+}
+
 // whether the 16-byte path applies: block width and row pitch multiples of the vector, aligned bases
 bool vec_ok(const SmParams& p, int dtype) {
   const int esz = dtype == SPARTA_F32 ? 4 : 2, E = 16 / esz;
@@ -256,6 +465,28 @@ bool vec_ok(const SmParams& p, int dtype) {
 template <bool BACKWARD>
 int launch(const SmParams& p, int batch, int dtype, cudaStream_t st) {
   dim3 grid((p.H + 7) / 8, batch), block(256);
+  if (!BACKWARD && vec_ok(p, dtype) && p.BH >= 4 * kRingWarps) {
+    const int rows_cta = kRingWarps * (kRingRows < p.BH / kRingWarps ? kRingRows : p.BH / kRingWarps);
+    const dim3 grid(p.H / rows_cta, batch), block(kRingWarps * 32);
+    constexpr int kSmem = kRingWarps * kRingBytes;
+    static SmemAttrOnce attr_f, attr_h, attr_b;
+    switch (dtype) {
+      case SPARTA_F32:
+        if (cudaError_t e = attr_f.ensure(softmax_fwd_ring_kernel<float>, kSmem); e != cudaSuccess) return (int)e;
+        softmax_fwd_ring_kernel<float><<<grid, block, kSmem, st>>>(p);
+        break;
+      case SPARTA_F16:
+        if (cudaError_t e = attr_h.ensure(softmax_fwd_ring_kernel<__half>, kSmem); e != cudaSuccess) return (int)e;
+        softmax_fwd_ring_kernel<__half><<<grid, block, kSmem, st>>>(p);
+        break;
+      case SPARTA_BF16:
+        if (cudaError_t e = attr_b.ensure(softmax_fwd_ring_kernel<__nv_bfloat16>, kSmem); e != cudaSuccess) return (int)e;
+        softmax_fwd_ring_kernel<__nv_bfloat16><<<grid, block, kSmem, st>>>(p);
+        break;
+      default: return SPARTA_ERR_BAD_ARG;
+    }
+    return launch_status();
+  }
   if (!BACKWARD && vec_ok(p, dtype)) {
     const dim3 grid((p.H + 3) / 4, batch), block(128);  // four rows per CTA measured 5 % faster than eight
     switch (dtype) {

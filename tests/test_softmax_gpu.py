@@ -139,3 +139,35 @@ def test_half_types_element_mask(dtype, compressed):
     torch.testing.assert_close(got_y.float().cpu(), want_y, rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(got_dx.float().cpu(), want_dx, rtol=2e-2, atol=2e-2)
     assert torch.all(got_y[:, 72:80] == 0)
+
+
+@pytest.mark.parametrize('dtype,W', [(torch.float16, 8192), (torch.bfloat16, 8192), (torch.float32, 4096)])
+@pytest.mark.parametrize('compressed', [True, False])
+@pytest.mark.parametrize('element_mask', [False, True])
+def test_row_lengths_across_the_forward_paths(dtype, W, compressed, element_mask):
+    """Block rows of very different lengths in one launch: a row that fits the registers (<= 4 KB of kept
+    values), one that is processed in the shared-memory ring (<= 12 KB), one longer than the ring (scalar
+    passes), and an empty one; 64-row blocks (sixteen rows per warp) and 16-row blocks (four)."""
+    esz = 4 if dtype == torch.float32 else 2
+    g = torch.Generator().manual_seed(W + esz)
+    for bh in (64, 16):
+        H = 4 * bh
+        x = (torch.randn((2, H, W), generator=g) * 2).to(dtype)
+        blocks = torch.zeros((4, W // 64), dtype=torch.uint8)
+        blocks[0, torch.randperm(W // 64, generator=g)[:3072 // esz // 64]] = 1        # 3 KB of kept values per row
+        blocks[1, torch.randperm(W // 64, generator=g)[:10240 // esz // 64]] = 1       # 10 KB
+        blocks[2] = 1                                                                   # 16 KB: the whole row
+        mask = blocks.repeat_interleave(bh, 0).repeat_interleave(64, 1)
+        if element_mask:
+            mask = mask * (torch.rand((H, W), generator=g) > 0.3).to(torch.uint8)
+            mask[bh + 3] = 0  # a fully masked row inside kept blocks
+        op = SparseSoftmax(mask.cuda(), 3.0, compressed=compressed)
+        op.build({'forward:y': params(bh, 64)}, sample_inputs=[x.cuda()])
+        ix = op.get_sparse_indexes('y')
+        xin = ix.convert(x.cuda()) if compressed else x.cuda()
+        out = op(xin)
+        got = ix.inverse(out) if compressed else out
+        want = oracle.softmax_forward_reference(x.float(), mask, 3.0)
+        tol = TOL if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(got.float().cpu(), want, **tol)
+        assert torch.all(got[:, 3 * bh:] == 0)
