@@ -260,14 +260,16 @@ __device__ __forceinline__ void softmax_row_in_registers(const SmParams& p, uint
 // the bytes an SM keeps in flight are bounded by its register file.  Here a warp owns up to kRingRows
 // rows of one block row (every kRingWarps-th row of its CTA's share) and a private ring in shared memory; it issues the asynchronous copies
 // (cp.async, 16 bytes per lane) of the rows up to `slots - 1` ahead of the one it computes, so about
-// 150 KB per SM are in flight whatever the warps are doing.  A lane copies, reads back and stores the
+// 100 KB per SM are in flight whatever the warps are doing.  Measured on 1.35 GB of compressed fp16 scores
+// (rows of 2.5 KB): 16 rows per warp with a 12 KB ring and four CTAs per SM 0.274 ms, 8 rows 0.250 ms, 8 rows with
+// an 8 KB ring and five CTAs 0.238 ms (the register-resident kernel above: 0.349 ms).  A lane copies, reads back and stores the
 // same 16-byte vectors, so the ring needs no barrier: its own wait_group orders the copy before the read,
 // and the read's register dependency orders it before the slot is refilled.  The offsets of a row are
 // those of the warp's first row plus a row step.  Used when block rows have at least 16 rows.
 // ---------------------------------------------------------------------------------------------------
-constexpr int kRingRows = 16;            // rows per warp at most; a CTA takes kRingWarps x rows consecutive rows of a block row
-constexpr int kRingBytes = 12 * 1024;    // ring capacity per warp
-constexpr int kRingWarps = 4;            // warps per CTA: 48 KB of shared memory, four CTAs per SM
+constexpr int kRingRows = 8;             // rows per warp at most; a CTA takes kRingWarps x rows consecutive rows of a block row
+constexpr int kRingBytes = 8 * 1024;     // ring capacity per warp
+constexpr int kRingWarps = 4;            // warps per CTA: 32 KB of shared memory, five CTAs per SM (96 registers)
 constexpr int kRingMaxSlots = 8;
 
 __device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gptr) {
@@ -342,7 +344,7 @@ __device__ __forceinline__ void softmax_row_in_shared(const SmParams& p, uint8_t
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kRingWarps * 32, 4) softmax_fwd_ring_kernel(SmParams p) {
+__global__ void __launch_bounds__(kRingWarps * 32, 5) softmax_fwd_ring_kernel(SmParams p) {
   constexpr int E = 16 / sizeof(T);
   extern __shared__ __align__(16) uint8_t ring_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -410,7 +412,7 @@ __global__ void __launch_bounds__(kRingWarps * 32, 4) softmax_fwd_ring_kernel(Sm
     cp_async_commit();
   };
   if (nv > 32 * kVecs) {
-    // Rows longer than the registers hold (up to the ring's 12 KB) stay in shared memory: the same pipeline,
+    // Rows longer than the registers hold (up to the ring's capacity) stay in shared memory: the same pipeline,
     // with the three passes reading and rewriting the row's slot.  A lane owns vectors lane, lane + 32, ...
     const uint32_t step = p.compressed ? p.BW : p.W;
     auto vec_off = [&](int v, int k) -> uint32_t {

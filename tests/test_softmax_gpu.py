@@ -146,8 +146,8 @@ def test_half_types_element_mask(dtype, compressed):
 @pytest.mark.parametrize('element_mask', [False, True])
 def test_row_lengths_across_the_forward_paths(dtype, W, compressed, element_mask):
     """Block rows of very different lengths in one launch: a row that fits the registers (<= 4 KB of kept
-    values), one that is processed in the shared-memory ring (<= 12 KB), one longer than the ring (scalar
-    passes), and an empty one; 64-row blocks (sixteen rows per warp) and 16-row blocks (four)."""
+    values), one that is processed in the shared-memory ring (<= 8 KB), one longer than the ring (scalar
+    passes), and an empty one; 64-row blocks (eight rows per warp) and 16-row blocks (four)."""
     esz = 4 if dtype == torch.float32 else 2
     g = torch.Generator().manual_seed(W + esz)
     for bh in (64, 16):
@@ -155,7 +155,7 @@ def test_row_lengths_across_the_forward_paths(dtype, W, compressed, element_mask
         x = (torch.randn((2, H, W), generator=g) * 2).to(dtype)
         blocks = torch.zeros((4, W // 64), dtype=torch.uint8)
         blocks[0, torch.randperm(W // 64, generator=g)[:3072 // esz // 64]] = 1        # 3 KB of kept values per row
-        blocks[1, torch.randperm(W // 64, generator=g)[:10240 // esz // 64]] = 1       # 10 KB
+        blocks[1, torch.randperm(W // 64, generator=g)[:7168 // esz // 64]] = 1        # 7 KB
         blocks[2] = 1                                                                   # 16 KB: the whole row
         mask = blocks.repeat_interleave(bh, 0).repeat_interleave(64, 1)
         if element_mask:
