@@ -43,24 +43,26 @@ __device__ __forceinline__ uint32_t zero_bytes(uint32_t w) {
   return (w - 0x01010101u) & ~w & 0x80808080u;
 }
 
-// In-place inclusive scan of p[1..n] (p[0] must be 0) by one CTA (any power-of-two size up to 256 threads).
+// In-place inclusive scan of p[1..n] (p[0] must be 0) by one CTA of up to 1024 threads: every thread sums a
+// chunk, the chunk sums are scanned with shuffles inside each warp and the warp totals through shared memory
+// (two barriers in all; s_part needs one word per warp).
 __device__ void block_scan_inplace(int32_t* p, int n, int32_t* s_part) {
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nt = blockDim.x;
   const int chunk = (n + nt - 1) / nt;
   const int lo = min(n, tid * chunk), hi = min(n, lo + chunk);
   int sum = 0;
   for (int i = lo; i < hi; ++i) sum += p[i + 1];
-  s_part[tid] = sum;
-  __syncthreads();
-  // Hillis-Steele over 256 partials
-  for (int off = 1; off < nt; off <<= 1) {
-    int v = tid >= off ? s_part[tid - off] : 0;
-    __syncthreads();
-    s_part[tid] += v;
-    __syncthreads();
+  int incl = sum;  // inclusive scan of the chunk sums within the warp
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += v;
   }
-  int run = s_part[tid] - sum;  // exclusive prefix of this thread's chunk
+  if (lane == 31) s_part[warp] = incl;
+  __syncthreads();
+  int run = incl - sum;  // exclusive prefix of this thread's chunk
+  for (int w = 0; w < warp; ++w) run += s_part[w];
   for (int i = lo; i < hi; ++i) {
     run += p[i + 1];
     p[i + 1] = run;
@@ -88,12 +90,11 @@ __device__ void phase2(const BcsParams& p, int b, const uint8_t* occ, int32_t* s
     if (threadIdx.x == 0) row_ptr[0] = 0;
     for (int r = warp; r < R; r += nwarp) {
       int cnt = 0;
-      for (int c = lane; c < Cn; c += 32) {
-        const int o = occ_at((size_t)r * Cn + c);
-        cnt += o & 1;
+      for (int c0 = 0; c0 < Cn; c0 += 32) {  // whole warps, so that every lane takes part in the ballot
+        const int o = c0 + lane < Cn ? occ_at((size_t)r * Cn + c0 + lane) : 0;
+        cnt += __popc(__ballot_sync(0xffffffffu, o & 1));
         nonuni |= o & 2;
       }
-      cnt = warp_sum_int(cnt);
       if (lane == 0) row_ptr[r + 1] = cnt;
     }
     __syncthreads();

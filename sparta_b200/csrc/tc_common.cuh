@@ -325,6 +325,7 @@ EncodeTiledFn encode_tiled_fn();
 
 constexpr int kTensorMapU8 = 100;   // dtype code for byte tensors (masks); SPARTA_F16 / SPARTA_BF16 otherwise
 constexpr int kTensorMapU32 = 101;  // bytes viewed as 32-bit words, which allows boxes up to 1 KB wide
+constexpr int kTensorMapU64 = 102;  // bytes viewed as 64-bit words: boxes up to 2 KB wide
 
 // rank-2 or rank-3 row-major tensor of 2-byte (or, with kTensorMapU8 / kTensorMapU32, 1- / 4-byte) elements; dims / box listed innermost first.
 // Returns a status code of sparta_b200.h.

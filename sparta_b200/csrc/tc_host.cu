@@ -33,6 +33,7 @@ int make_tensor_map(CUtensorMap* map, const void* base, int dtype, int rank, con
   else if (dtype == SPARTA_BF16) dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   else if (dtype == kTensorMapU8) dt = CU_TENSOR_MAP_DATA_TYPE_UINT8;
   else if (dtype == kTensorMapU32) dt = CU_TENSOR_MAP_DATA_TYPE_UINT32;
+  else if (dtype == kTensorMapU64) dt = CU_TENSOR_MAP_DATA_TYPE_UINT64;
   else return SPARTA_ERR_UNSUPPORTED;
   cuuint64_t d[5], s[4];
   cuuint32_t b[5], e[5];
