@@ -44,7 +44,7 @@ SPARSITY = 0.75
 # dram__bytes_read.sum + dram__bytes_write.sum of one bsmm_dsd_tc_kernel launch on this workload
 # (profiles/bsmm_dsd_tc_linear4096_sp75.md); algorithmic bytes are 75.5 MB
 DSD75_TRAFFIC_BYTES = 46.17e6
-E2E_CHUNK = 512  # token rows per chunk of the end-to-end pipeline
+E2E_CHUNK = 1024  # token rows per chunk of the end-to-end pipeline (measured with graph replay: 512 rows 1.00 ms, 1024 rows 0.945 ms, 2048 rows 1.02 ms per step)
 
 
 def load_peaks():
@@ -712,7 +712,7 @@ def main():
     x_host = wl['x'].pin_memory()
     y_host = torch.empty((TOKENS, OUT_F), dtype=torch.float16).pin_memory()
     chunk = build_linear(device, SPARSITY, 'dsd', tokens=E2E_CHUNK, like=wl)
-    streamed = sparta.nn.HostStreamedRows(chunk['op'], E2E_CHUNK)
+    streamed = sparta.nn.HostStreamedRows(chunk['op'], E2E_CHUNK, graph=True)
 
     def e2e_step():
         streamed(x_host, y_host)
@@ -773,7 +773,7 @@ def main():
             'e2e': {'value': e2e_value, 'unit': 'TFLOP/s', 'ms_per_step': e2e_ms / args.steps,
                     'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': d2h_bytes,
                     'how': f'SparseLinear built for {E2E_CHUNK} rows, called through sparta.nn.HostStreamedRows: '
-                           f'{TOKENS // E2E_CHUNK} chunks, copy-in / kernel / copy-out overlapped on three streams'},
+                           f'{TOKENS // E2E_CHUNK} chunks, copy-in / kernel / copy-out overlapped on three streams, the sequence replayed from a CUDA graph'},
             'gpu_launches': args.steps,
             'clocks': clocks,
             'ranks': ranks,

@@ -18,17 +18,25 @@ class HostStreamedRows(object):
             e.g. a ``SparseLinear`` built with a ``chunk_rows``-row sample input.
         chunk_rows: rows per chunk; the host tensor's row count must be a multiple of it.
         depth: device input buffers kept in flight.
+        graph: capture the whole sequence (copies, kernels and their cross-stream dependencies) in a CUDA
+            graph on the first call for a pair of host buffers and replay it afterwards: one launch instead
+            of about a dozen host calls per chunk.  The host buffers' addresses are baked into the graph, so
+            a different buffer (or shape) captures anew; a capture that fails falls back to plain launches.
 
     ``__call__(x_host, y_host)`` enqueues everything relative to the current stream: work starts after
     what the current stream already holds and the current stream waits for the last copy out, so events
     or a synchronize on the current stream bracket the whole transfer + compute.
     """
 
-    def __init__(self, op: Callable[[torch.Tensor], torch.Tensor], chunk_rows: int, depth: int = 2):
+    def __init__(self, op: Callable[[torch.Tensor], torch.Tensor], chunk_rows: int, depth: int = 2,
+                 graph: bool = False):
         assert chunk_rows > 0 and depth >= 1
         self._op = op
         self._rows = chunk_rows
         self._depth = depth
+        self._use_graph = graph
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self._graph_key = None
         self._bufs: Optional[List[torch.Tensor]] = None
         self._s_in: Optional[torch.cuda.Stream] = None
         self._s_out: Optional[torch.cuda.Stream] = None
@@ -46,6 +54,26 @@ class HostStreamedRows(object):
         assert n % self._rows == 0, f'{n} rows are not a multiple of the chunk size {self._rows}'
         assert y_host.shape[0] == n
         device = device or torch.device('cuda', torch.cuda.current_device())
+        if not self._use_graph:
+            return self._enqueue(x_host, y_host, device)
+        key = (x_host.data_ptr(), y_host.data_ptr(), tuple(x_host.shape), tuple(y_host.shape), x_host.dtype, device)
+        if self._graph is None or self._graph_key != key:
+            self._enqueue(x_host, y_host, device)  # plain first pass: buffers, lazy initialisation in the operator
+            torch.cuda.synchronize(device)
+            graph = torch.cuda.CUDAGraph()
+            try:
+                with torch.cuda.graph(graph):
+                    self._enqueue(x_host, y_host, device)
+            except Exception:  # e.g. an operator that synchronises or allocates outside the graph's pool
+                self._use_graph = False
+                torch.cuda.synchronize(device)
+                return self._enqueue(x_host, y_host, device)
+            self._graph, self._graph_key = graph, key
+        self._graph.replay()
+        return y_host
+
+    def _enqueue(self, x_host: torch.Tensor, y_host: torch.Tensor, device: torch.device):
+        n = x_host.shape[0]
         self._prepare(x_host, device)
         cur = torch.cuda.current_stream(device)
         start = torch.cuda.Event()

@@ -35,6 +35,39 @@ def test_streamed_rows_match_single_call(chunks, depth):
         assert torch.equal(y_host, whole)
 
 
+def test_streamed_rows_replayed_from_a_graph():
+    """graph=True: the second and later calls replay the captured sequence; new host buffers capture anew;
+    an operator that cannot be captured (it synchronises) falls back to plain launches."""
+    rows, K, N, chunks = 1024, 256, 384, 4
+    g = torch.Generator().manual_seed(8)
+    mask = oracle.block_mask((N, K), (32, 32), 0.6, generator=g).cuda()
+    dense = torch.nn.Linear(K, N, device='cuda', dtype=torch.float16)
+    whole_op = _linear(rows, K, N, mask, dense)
+    streamed = sparta.nn.HostStreamedRows(_linear(rows // chunks, K, N, mask, dense), rows // chunks, graph=True)
+    for trial in range(2):  # two different pairs of host buffers
+        x = torch.randn((rows, K), generator=g).half()
+        x_host, y_host = x.pin_memory(), torch.empty((rows, N), dtype=torch.float16).pin_memory()
+        for call in range(3):
+            if call == 2:  # new contents in the same buffers: the graph reads them at replay time
+                x_host.copy_(torch.randn((rows, K), generator=g).half())
+            y_host.zero_()
+            streamed(x_host, y_host)
+            torch.cuda.synchronize()
+            assert torch.equal(y_host, whole_op(x_host.cuda()).cpu())
+        assert streamed._graph is not None
+
+    def syncing_op(t):
+        torch.cuda.synchronize()
+        return t * 2
+    fallback = sparta.nn.HostStreamedRows(syncing_op, 256, graph=True)
+    x_host, y_host = torch.ones((512, 8)).pin_memory(), torch.empty((512, 8)).pin_memory()
+    for _ in range(2):
+        fallback(x_host, y_host)
+        torch.cuda.synchronize()
+        assert torch.all(y_host == 2)
+    assert fallback._graph is None
+
+
 def test_streamed_rows_rejects_bad_inputs():
     streamed = sparta.nn.HostStreamedRows(lambda t: t, 128)
     x = torch.zeros((256, 8)).pin_memory()
