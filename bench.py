@@ -605,6 +605,24 @@ def attention_c5_sharded(device, world, rank, peaks, barrier):
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         gather = {'allgather_bytes_received_per_rank': received, 'allgather_own_shard_intact': bool(flag.item()),
                   'collective': 'NCCL all_gather_into_tensor over NVLink / NVSwitch'}
+        # the same exchange folded into the attention kernel: every output tile is also stored, from shared memory
+        # with bulk tensor stores over NVLink, into this rank's slice of every peer's gathered output (symmetric
+        # memory), so the transfer overlaps the remaining tiles' compute and O is not read again
+        try:
+            gathered = parallel.GatheredHeads(heads, S, D, o.dtype, device)
+            with torch.no_grad():
+                step = lambda: attn.forward_gathered(q, k, v, gathered.local, gathered.peer_addresses)
+                local['fused_gather_ms'] = time_steps(step, 3, 2, no_flush, barrier) / 3
+            same = bool(torch.equal(gathered.wait(), full))
+            flag = torch.tensor([1 if same else 0], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            gather['fused_gather'] = {'how': 'attention kernel stores each tile to O and to the peers\' buffers (peer memory, '
+                                             'cp.async.bulk.tensor stores over NVLink); no separate collective',
+                                      'equals_nccl_allgather_bitwise': bool(flag.item())}
+            del gathered
+        except Exception as e:
+            gather['fused_gather'] = {'error': repr(e)[:200]}
+            local['fused_gather_ms'] = -1.0  # every rank reports the same keys
         del full
     stats = rank_summary(local, world, device)
     flops = 4.0 * heads_total * nnz * 64 * 64 * D
@@ -615,6 +633,9 @@ def attention_c5_sharded(device, world, rank, peaks, barrier):
     for name in ('allgather_ms', 'allgather_in_gbs'):
         if name in stats:
             out[name] = stats[name]
+    if 'fused_gather_ms' in stats and stats['fused_gather_ms']['min'] >= 0 and 'error' not in out['fused_gather']:
+        out['fused_gather']['ms'] = stats['fused_gather_ms']
+        out['fused_gather']['separate_passes_ms'] = round(stats['fwd_ms']['max'] + stats['allgather_ms']['max'], 4)
     del q, k, v, o, attn
     torch.cuda.empty_cache()
     return out

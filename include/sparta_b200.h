@@ -227,6 +227,21 @@ int sparta_attn_fwd(const void* Q, const void* K, const void* V, void* O, const 
                     int heads, int Nt, int Ns, int D, int BLK, int dtype, float* lse,
                     int32_t* status, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same forward with the all-gather of the outputs fused into it, for heads sharded over the GPUs of one
+ * box (no counterpart in the reference, which has no multi-GPU code; the configuration "sharded by
+ * batch x head with outputs all-gathered over NVLink" ends in this exchange).  copies[0 .. n_copies-1] are
+ * device addresses -- normally in peers' memory, mapped into this process (symmetric memory, IPC) -- laid
+ * out like O: every output tile is stored to O and, from shared memory with bulk tensor stores, to each
+ * copy, so the transfer over NVLink overlaps the remaining tiles' compute and no separate collective pass
+ * reads O again.  The copies are complete when the kernel is; peers learn of it by whatever barrier the
+ * caller uses between ranks.  Covered: D = 128 with Nt a multiple of 256 (SPARTA_ERR_UNSUPPORTED
+ * otherwise: gather with a collective instead); n_copies <= SPARTA_ATTN_MAX_COPIES. */
+#define SPARTA_ATTN_MAX_COPIES 7
+int sparta_attn_fwd_gather(const void* Q, const void* K, const void* V, void* O, const int32_t* row_ptr,
+                           const int32_t* bcsr_idx, const int32_t* nnz, const uint8_t* mask, float scale,
+                           int heads, int Nt, int Ns, int D, int BLK, int dtype, float* lse,
+                           int32_t* status, void* const* copies, int n_copies, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Tile table: what sparta.nn.tune searches over in the reference
  * (sparta/specializer/kernels/look_up_tables/sparta_matmul_lut.csv, sparta/nn/module_tuner.py:169)

@@ -73,6 +73,9 @@ SIGNATURES = {
     'sparta_attn_fwd': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                 c_void_p, c_void_p, c_size_t, c_void_p]),
+    'sparta_attn_fwd_gather': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                       c_void_p, POINTER(c_void_p), c_int, c_void_p]),
     'sparta_last_status': (c_int, [POINTER(c_int32)]),
     'sparta_tile_table': (c_int, [c_int, c_int, POINTER(TileEntry), c_int]),
 }

@@ -511,11 +511,35 @@ using namespace sparta;
 
 extern "C" size_t sparta_attn_fwd_workspace_bytes(int, int, int, int, int) { return 0; }
 
+namespace {
+int attn_fwd_entry(const void* Q, const void* K, const void* V, void* O, const int32_t* row_ptr,
+                   const int32_t* bcsr_idx, const uint8_t* mask, float scale, int heads, int Nt, int Ns, int D,
+                   int BLK, int dtype, float* lse, int32_t* status, void* const* copies, int n_copies, void* stream);
+}
+
 extern "C" int sparta_attn_fwd(const void* Q, const void* K, const void* V, void* O, const int32_t* row_ptr,
                                const int32_t* bcsr_idx, const int32_t* nnz, const uint8_t* mask, float scale,
                                int heads, int Nt, int Ns, int D, int BLK, int dtype, float* lse,
                                int32_t* status, void* workspace, size_t workspace_bytes, void* stream) {
   (void)nnz; (void)workspace; (void)workspace_bytes;
+  return attn_fwd_entry(Q, K, V, O, row_ptr, bcsr_idx, mask, scale, heads, Nt, Ns, D, BLK, dtype, lse, status, nullptr, 0,
+                        stream);
+}
+
+extern "C" int sparta_attn_fwd_gather(const void* Q, const void* K, const void* V, void* O, const int32_t* row_ptr,
+                                      const int32_t* bcsr_idx, const int32_t* nnz, const uint8_t* mask, float scale,
+                                      int heads, int Nt, int Ns, int D, int BLK, int dtype, float* lse,
+                                      int32_t* status, void* const* copies, int n_copies, void* stream) {
+  (void)nnz;
+  if (n_copies < 0 || n_copies > SPARTA_ATTN_MAX_COPIES || (n_copies > 0 && !copies)) return SPARTA_ERR_BAD_ARG;
+  return attn_fwd_entry(Q, K, V, O, row_ptr, bcsr_idx, mask, scale, heads, Nt, Ns, D, BLK, dtype, lse, status, copies,
+                        n_copies, stream);
+}
+
+namespace {
+int attn_fwd_entry(const void* Q, const void* K, const void* V, void* O, const int32_t* row_ptr,
+                   const int32_t* bcsr_idx, const uint8_t* mask, float scale, int heads, int Nt, int Ns, int D,
+                   int BLK, int dtype, float* lse, int32_t* status, void* const* copies, int n_copies, void* stream) {
   if (!Q || !K || !V || !O || !row_ptr || !bcsr_idx || heads <= 0 || Nt <= 0 || Ns <= 0) return SPARTA_ERR_BAD_ARG;
   if (dtype != SPARTA_F16 && dtype != SPARTA_BF16) return SPARTA_ERR_UNSUPPORTED;
   if (BLK != kBlk || (D != 64 && D != 128)) return SPARTA_ERR_UNSUPPORTED;
@@ -535,8 +559,11 @@ extern "C" int sparta_attn_fwd(const void* Q, const void* K, const void* V, void
   // D = 128: two Q tiles per CTA sharing the K / V tiles (attn_tc2.cu), when the query length allows it.  D = 64
   // stays with one tile per CTA and two CTAs per SM, which measured 25 % faster than the two-tile form there.
   if (D == 128 && attn_tc2_supported(Nt))
-    return attn_tc2_launch(Q, K, V, O, row_ptr, bcsr_idx, mask, p.scale_log2, heads, Nt, Ns, D, dtype, lse, p.status, st);
+    return attn_tc2_launch(Q, K, V, O, row_ptr, bcsr_idx, mask, p.scale_log2, heads, Nt, Ns, D, dtype, lse, p.status,
+                           copies, n_copies, st);
+  if (n_copies > 0) return SPARTA_ERR_UNSUPPORTED;  // the one-tile kernel stores O only
   const int fmt = dtype == SPARTA_F16 ? 0 : 1;
   if (D == 64) return fmt == 0 ? launch_attn<64, 0>(Q, K, V, p, dtype, st) : launch_attn<64, 1>(Q, K, V, p, dtype, st);
   return fmt == 0 ? launch_attn<128, 0>(Q, K, V, p, dtype, st) : launch_attn<128, 1>(Q, K, V, p, dtype, st);
 }
+}  // namespace

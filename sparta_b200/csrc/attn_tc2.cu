@@ -25,6 +25,7 @@
 //   warp 17     issues all MMAs: Q.K^T (M128 N128, D/16 per tile and step) and P.V (M128 N=D, A from tensor
 //               memory, V MN-major in shared memory); a tile's next Q.K^T goes out right behind its P.V
 // All mbarrier waits are bounded (status words of sparta_last_status).
+#include <cstring>
 #include <type_traits>
 
 #include "bsmm.cuh"
@@ -77,6 +78,15 @@ struct Attn2Params {
   int grouped;          // launch order, see the kernel
   float scale_log2;     // scale * log2(e)
   int32_t* status;
+  int n_copies;         // further destinations of O (the peers' gathered outputs), see GatherMaps
+};
+
+// Tensor maps of the further destinations of O, each laid out like O itself ([heads * Nt, D]): with the heads
+// sharded over GPUs, a rank's output is also stored into its slice of every peer's gathered output, over
+// NVLink, from the kernel that computes it.  The tile is staged in the (by then idle) shared memory of its
+// Q tile in the 128-byte swizzle and leaves as bulk tensor stores, so that the link carries full lines.
+struct GatherMaps {
+  CUtensorMap m[SPARTA_ATTN_MAX_COPIES];
 };
 
 template <int D>
@@ -94,7 +104,7 @@ struct Cfg2 {
 template <int D, int FMT>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, Attn2Params p) {
+                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ GatherMaps gm, Attn2Params p) {
   using T = typename std::conditional<FMT == 0, __half, __nv_bfloat16>::type;
   using C = Cfg2<D>;
   constexpr int kChunks = C::kChunks;
@@ -511,6 +521,13 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     failed |= !ok;
     if (!ok && lane == 0) atomicExch(&p.status[3], 1);
     tc_fence_after_sync();
+    // the staging tile below reuses the Q tile's shared memory: its load must have landed (it has, unless this
+    // tile took part in no step), and "P.V complete" above covers the last MMA that read it
+    if (p.n_copies > 0 && count > 0 && !mbar_wait_warp(q_full, 0)) {
+      ok = false;
+      failed = true;
+      if (lane == 0) atomicExch(&p.status[3], 1);
+    }
     s_lsum[tile][colhalf][row] = l_run;  // the row sum is the two threads' partial sums
     named_barrier_sync(bar_id, kSmWarps * 32);
     l_run += s_lsum[tile][colhalf ^ 1][row];
@@ -542,6 +559,25 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
       for (int q = 0; q < 4; ++q)
         dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      if (p.n_copies > 0) {
+        // the same 64 bytes into the staging tile: 64-column chunk c / 2, row `row`, 16-byte pieces
+        // (c & 1) * 4 .. + 3 at piece position ^ (row & 7)
+        uint8_t* srow = q_s + tile * C::kQBytes + (c >> 1) * (kTileM * 128) + row * 128;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(srow + (((((c & 1) << 2) | q) ^ (row & 7)) << 4)) =
+              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      }
+    }
+    if (p.n_copies > 0) {  // uniform over the CTA
+      fence_proxy_async_smem();  // the staging tile was written through the generic proxy, TMA reads through the async one
+      named_barrier_sync(bar_id, kSmWarps * 32);
+      if (wt == 0 && lane == 0) {
+        for (int g = 0; g < p.n_copies; ++g)
+          for (int ch = 0; ch < kChunks; ++ch)
+            tma_store_2d(&gm.m[g], q_s + tile * C::kQBytes + ch * (kTileM * 128), ch * 64, (int)(q_row0 + tile * kTileM));
+        tma_store_commit_and_wait_all();  // the peers' copies are complete when the kernel ends
+      }
     }
     if (p.lse && colhalf == 0) {
       // natural-log sum of exponentials of the scaled scores (-inf for a fully masked row)
@@ -558,9 +594,19 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 }
 
 template <int D, int FMT>
-int launch_attn2(const void* Q, const void* K, const void* V, const Attn2Params& p, int dtype, cudaStream_t st) {
+int launch_attn2(const void* Q, const void* K, const void* V, const Attn2Params& p, void* const* copies, int dtype,
+                 cudaStream_t st) {
   using C = Cfg2<D>;
   CUtensorMap tm_q, tm_k, tm_v;
+  GatherMaps gm;
+  std::memset(&gm, 0, sizeof(gm));
+  for (int g = 0; g < p.n_copies; ++g) {
+    const uint64_t dims[2] = {(uint64_t)D, (uint64_t)p.heads * p.Nt};
+    const uint64_t pitch[1] = {(uint64_t)D * 2};
+    const uint32_t box[2] = {64, kTileM};
+    int rc = make_tensor_map(&gm.m[g], copies[g], dtype, 2, dims, pitch, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != SPARTA_OK) return rc;
+  }
   const uint64_t strides[1] = {(uint64_t)D * 2};
   {
     const uint64_t dims[2] = {(uint64_t)D, (uint64_t)p.heads * p.Nt};
@@ -580,7 +626,7 @@ int launch_attn2(const void* Q, const void* K, const void* V, const Attn2Params&
   static SmemAttrOnce attr;
   if (cudaError_t e = attr.ensure(kern, C::kSmem); e != cudaSuccess) return static_cast<int>(e);
   dim3 grid((unsigned)((long long)p.heads * (p.Nt / (kTiles * kTileM))));
-  kern<<<grid, kThreads, C::kSmem, st>>>(tm_q, tm_k, tm_v, p);
+  kern<<<grid, kThreads, C::kSmem, st>>>(tm_q, tm_k, tm_v, gm, p);
   return launch_status();
 }
 
@@ -595,16 +641,20 @@ bool attn_tc2_supported(int Nt) { return Nt % (kTiles * kTileM) == 0; }
 
 int attn_tc2_launch(const void* Q, const void* K, const void* V, void* O, const int32_t* row_ptr,
                     const int32_t* bcsr_idx, const uint8_t* mask, float scale_log2, int heads, int Nt, int Ns,
-                    int D, int dtype, float* lse, int32_t* status, cudaStream_t st) {
+                    int D, int dtype, float* lse, int32_t* status, void* const* copies, int n_copies, cudaStream_t st) {
+  if (n_copies < 0 || n_copies > SPARTA_ATTN_MAX_COPIES || (n_copies > 0 && !copies)) return SPARTA_ERR_BAD_ARG;
+  for (int g = 0; g < n_copies; ++g)
+    if (!copies[g] || !aligned(copies[g], 16)) return SPARTA_ERR_ALIGN;
   Attn2Params p;
+  p.n_copies = n_copies;
   p.row_ptr = row_ptr; p.idx = bcsr_idx; p.mask = mask; p.O = O; p.lse = lse;
   p.Nt = Nt; p.Ns = Ns; p.heads = heads;
   p.grouped = kv_exceeds_l2(heads, Ns, D);
   p.scale_log2 = scale_log2;
   p.status = status;
   const int fmt = dtype == SPARTA_F16 ? 0 : 1;
-  if (D == 64) return fmt == 0 ? launch_attn2<64, 0>(Q, K, V, p, dtype, st) : launch_attn2<64, 1>(Q, K, V, p, dtype, st);
-  return fmt == 0 ? launch_attn2<128, 0>(Q, K, V, p, dtype, st) : launch_attn2<128, 1>(Q, K, V, p, dtype, st);
+  if (D == 64) return fmt == 0 ? launch_attn2<64, 0>(Q, K, V, p, copies, dtype, st) : launch_attn2<64, 1>(Q, K, V, p, copies, dtype, st);
+  return fmt == 0 ? launch_attn2<128, 0>(Q, K, V, p, copies, dtype, st) : launch_attn2<128, 1>(Q, K, V, p, copies, dtype, st);
 }
 
 }  // namespace sparta

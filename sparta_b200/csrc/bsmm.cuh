@@ -45,7 +45,7 @@ bool attn_tc2_supported(int Nt);
 bool kv_exceeds_l2(int heads, int Ns, int D);
 int attn_tc2_launch(const void* Q, const void* K, const void* V, void* O, const int32_t* row_ptr,
                     const int32_t* bcsr_idx, const uint8_t* mask, float scale_log2, int heads, int Nt, int Ns,
-                    int D, int dtype, float* lse, int32_t* status, cudaStream_t st);
+                    int D, int dtype, float* lse, int32_t* status, void* const* copies, int n_copies, cudaStream_t st);
 
 // whether the tcgen05 matmul / fused attention kernels are compiled into this build
 bool bsmm_tc_available();

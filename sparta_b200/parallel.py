@@ -3,10 +3,12 @@
 The path has no exchange step: attention shards by batch x head (the leading dimension of
 ``[B*H, N, E]`` tensors), SparseLinear by token rows; masks, indexes and weights are replicated, every
 rank builds its indexes locally.  The only collective offered is an optional all-gather of the
-outputs (NCCL over NVLink through ``torch.distributed``; gloo works for CPU tests).  The reference has
-no multi-GPU code; this module is an extension.
+outputs: as a separate pass (NCCL over NVLink through ``torch.distributed``; gloo works for CPU tests), or,
+for the fused attention kernel, folded into the kernel itself: ``GatheredHeads`` holds the full output in
+symmetric memory and the kernel stores every tile into the peers' buffers as it finishes it.  The
+reference has no multi-GPU code; this module is an extension.
 """
-from typing import Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -82,3 +84,36 @@ def all_gather_outputs(local: torch.Tensor, group: Optional[dist.ProcessGroup] =
     out = torch.empty((world * most,) + local.shape[1:], dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(out, padded, group=group)
     return torch.cat([out[r * most:r * most + n] for r, n in enumerate(sizes)], dim=0)
+
+
+class GatheredHeads(object):
+    """The all-gathered output ``[world * heads, N, E]`` of head-sharded attention, one copy per rank in
+    symmetric memory (``torch.distributed._symmetric_memory``: every rank's buffer is mapped into every
+    other rank's address space, NVLink peer access).
+
+    ``local`` is this rank's slice of its own buffer (pass it as the kernel's output); ``peer_addresses`` are
+    the device addresses of the same slice in every other rank's buffer (pass them as the kernel's copies:
+    ``SparseAttention.forward_gathered``).  ``wait()`` completes the exchange: this rank's stores are done
+    when its kernel is, and a barrier tells every rank that all the others are done too; after it ``full``
+    holds all heads on every rank.  Equal shards only.
+    """
+
+    def __init__(self, heads_per_rank: int, n: int, e: int, dtype: torch.dtype, device: torch.device,
+                 group: Optional[dist.ProcessGroup] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = dist.group.WORLD if group is None else group
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.shape = (self.world * heads_per_rank, n, e)
+        self.full = symm_mem.empty(self.shape, dtype=dtype, device=device)
+        self._handle = symm_mem.rendezvous(self.full, self.group)
+        lo, hi = self.rank * heads_per_rank, (self.rank + 1) * heads_per_rank
+        self.local = self.full[lo:hi]
+        offset = lo * n * e * self.full.element_size()
+        self.peer_addresses: List[int] = [int(self._handle.buffer_ptrs[r]) + offset
+                                          for r in range(self.world) if r != self.rank]
+
+    def wait(self):
+        torch.cuda.current_stream(self.full.device).synchronize()
+        dist.barrier(group=self.group)
+        return self.full

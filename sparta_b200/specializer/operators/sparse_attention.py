@@ -83,7 +83,17 @@ class SparseAttention(OperatorBase):
         sm = self._softmax.forward(qk)
         return self._matmul_out.forward(sm, value)
 
-    def _fused_forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    def forward_gathered(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                         out: torch.Tensor, copies: List[int]) -> torch.Tensor:
+        """Fused forward (no autograd) that writes the result into ``out`` and, tile by tile from the same
+        kernel, into every address of ``copies``: device addresses of buffers laid out like ``out``,
+        normally this rank's slice of the peers' gathered outputs (``sparta_b200.parallel.GatheredHeads``).
+        Raises when the fused kernel for this shape cannot store copies (gather with a collective then)."""
+        assert self.ready and self._use_fused, 'forward_gathered needs an operator built on the fused kernel'
+        return self._fused_forward(query.detach(), key.detach(), value.detach(), out=out, copies=copies)
+
+    def _fused_forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
+                       copies: Optional[List[int]] = None) -> torch.Tensor:
         _lib.require_cuda(q, k, v)
         idx = self._sparse_port.indexes
         shape = q.shape
@@ -92,13 +102,30 @@ class SparseAttention(OperatorBase):
         k = k.reshape(-1, self._Ns, E).contiguous()
         v = v.reshape(-1, self._Ns, E).contiguous()
         heads = q.shape[0]
-        out = torch.empty_like(q)
+        if out is None:
+            out = torch.empty_like(q)
+        else:
+            assert out.is_contiguous() and out.dtype == q.dtype and out.numel() == q.numel() and out.device == q.device
         L = _lib.lib()
         ws_bytes = L.sparta_attn_fwd_workspace_bytes(heads, self._Nt, self._Ns, E, FUSED_BLOCK)
         if self._attn_ws is None or self._attn_ws.numel() < ws_bytes or self._attn_ws.device != q.device:
             self._attn_ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device=q.device)
             self._attn_status = torch.zeros(4, dtype=torch.int32, device=q.device)
         mask = None if idx.block_uniform else idx.raw_mask
+        if copies:
+            import ctypes
+            addresses = (ctypes.c_void_p * len(copies))(*copies)
+            with torch.cuda.device(q.device):
+                _lib.check(L.sparta_attn_fwd_gather(
+                    q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                    idx.row_ptr.data_ptr(), idx.bcsr_buf.data_ptr(), idx.nnz_dev.data_ptr(),
+                    _lib.ptr(mask), float(self._scale), heads, self._Nt, self._Ns, E, FUSED_BLOCK,
+                    _lib.dtype_code(q), None, self._attn_status.data_ptr(), addresses, len(copies),
+                    _lib.stream_ptr(q.device)), 'sparta_attn_fwd_gather')
+            if self.check_status and any(self.fused_status()):
+                raise RuntimeError(f'fused sparse attention: a bounded wait ran out on the device, status words '
+                                   f'{self.fused_status()}; the output is invalid')
+            return out.reshape(shape)
         with torch.cuda.device(q.device):
             _lib.check(L.sparta_attn_fwd(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),

@@ -179,3 +179,30 @@ def test_fused_attention_odd_tile_count(dtype, E):
     g = torch.Generator().manual_seed(21)
     mask = oracle.block_mask((384, 640), (64, 64), 0.5, generator=g)
     _fused_case(dtype, E, 3, 384, 640, mask, seed=22)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_fused_attention_with_copies_of_the_output(dtype):
+    """The forward that also stores every output tile to further buffers (the peers' gathered outputs when
+    heads are sharded; here two more buffers on the same GPU): all destinations hold the same bits as the
+    plain forward, including tiles without any block (zeros) and with an element mask."""
+    from sparta_b200 import _lib
+    g = torch.Generator().manual_seed(12)
+    mask = oracle.block_mask((512, 768), (64, 64), 0.6, generator=g)
+    mask[64:128] = 0
+    mask[256:512] = 0                      # a whole pair of Q tiles without any block
+    fine = oracle.block_mask((512, 768), (8, 8), 0.3, generator=g)
+    for m in (mask, mask * fine):
+        op, (q, k, v) = _fused_case(dtype, 128, 3, 512, 768, m)
+        want = op(q.cuda(), k.cuda(), v.cuda())
+        full = torch.full((3, 3, 512, 128), 7.0, dtype=dtype, device='cuda')  # [destination, heads, Nt, E]
+        out = op.forward_gathered(q.cuda(), k.cuda(), v.cuda(), full[0], [full[1].data_ptr(), full[2].data_ptr()])
+        assert op.fused_status() == [0, 0, 0, 0]
+        assert out.data_ptr() == full[0].data_ptr()
+        for d in range(3):
+            assert torch.equal(full[d], want), f'destination {d}'
+    # the one-tile kernel (E = 64, or an odd number of Q tiles) stores O only and says so
+    op, (q, k, v) = _fused_case(dtype, 64, 1, 256, 256, torch.ones((256, 256), dtype=torch.uint8))
+    buf = torch.empty((2, 1, 256, 64), dtype=dtype, device='cuda')
+    with pytest.raises(_lib.SpartaError):
+        op.forward_gathered(q.cuda(), k.cuda(), v.cuda(), buf[0], [buf[1].data_ptr()])
