@@ -422,8 +422,8 @@ def run_extras(device, peaks, flush, only=None):
         sop = sparta.nn.SparseSoftmax(amask, 8.0, compressed=True)
         dg = torch.Generator(device=device).manual_seed(7)
         xd = torch.randn((heads, S, S), generator=dg, device=device, dtype=torch.float16)
-        sop.build({'forward:y': {'_impl': 'sparta', 'BLOCK_SIZE_H_VALUE': 64, 'BLOCK_SIZE_W_VALUE': 64,
-                                 'ROW_TILE_VALUE': 4}}, sample_inputs=[xd])
+        tile = {'_impl': 'sparta', 'BLOCK_SIZE_H_VALUE': 64, 'BLOCK_SIZE_W_VALUE': 64, 'ROW_TILE_VALUE': 4}
+        sop.build({'forward:y': tile, 'backward:x': tile}, sample_inputs=[xd])
         six = sop.get_sparse_indexes('y')
         xc = six.convert(xd)
         del xd
@@ -431,10 +431,15 @@ def run_extras(device, peaks, flush, only=None):
         nbytes = 2.0 * heads * nnz * 64 * 64 * 2  # read x + write y, kept blocks only (1.35 GB: larger than L2)
         with torch.no_grad():
             ms = time_steps(lambda: sop(xc), 5, 3, lambda: None) / 5
+            yc = sop(xc)
+            gc = torch.randn(xc.shape, generator=dg, device=device, dtype=torch.float16)
+            bwd_ms = time_steps(lambda: sop._sparse_ctx.backward(gc, yc), 5, 3, lambda: None) / 5
         extras['softmax_b4h16s4096_compressed'] = {
             'fwd_ms': round(ms, 4), 'nnz_blocks': nnz, 'gbs': round(nbytes / ms / 1e6, 1),
-            'frac_hbm_peak': round(nbytes / ms / 1e6 / peaks['hbm_gbs'], 4), 'l2': 'operands (1.35 GB) larger than L2, no flush'}
-        del xc, sop
+            'frac_hbm_peak': round(nbytes / ms / 1e6 / peaks['hbm_gbs'], 4), 'l2': 'operands (1.35 GB) larger than L2, no flush',
+            'bwd_ms': round(bwd_ms, 4), 'bwd_gbs': round(1.5 * nbytes / bwd_ms / 1e6, 1),  # reads dy and y, writes dx
+            'bwd_frac_hbm_peak': round(1.5 * nbytes / bwd_ms / 1e6 / peaks['hbm_gbs'], 4)}
+        del xc, yc, gc, sop
     except Exception as e:
         extras['softmax_b4h16s4096_compressed'] = {'error': repr(e)[:200]}
 

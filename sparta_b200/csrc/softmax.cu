@@ -452,11 +452,194 @@ __global__ void __launch_bounds__(kRingWarps * 32, 5) softmax_fwd_ring_kernel(Sm
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Backward pass through the same kind of ring: dx = y (dy - sum(dy y)) / T per row.  A slot holds the row of
+// dy followed by the row of y; both are read back into registers (64 of them), the dot product and the
+// result are formed in fp32, and dx is stored from registers.  Rows beyond the registers' 4 KB are processed
+// in the slot itself (up to 8 KB each); longer ones take scalar passes.  Masked elements: y is zeroed where the element mask is, which zeroes their terms and results.
+// ---------------------------------------------------------------------------------------------------
+constexpr int kBwdRingBytes = 16 * 1024;  // per warp: 64 KB per CTA, three CTAs per SM
+
+template <typename T>
+__global__ void __launch_bounds__(kRingWarps * 32, 3) softmax_bwd_ring_kernel(SmParams p) {
+  constexpr int E = 16 / sizeof(T);
+  extern __shared__ __align__(16) uint8_t ring_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows_w = min(kRingRows, p.BH / kRingWarps);
+  const int row0 = blockIdx.x * kRingWarps * rows_w + warp;
+  if (row0 >= p.H) return;
+  const long long bstride = p.compressed ? p.val_stride_blocks * p.BH * p.BW : (long long)p.H * p.W;
+  const T* dy = static_cast<const T*>(p.x) + (long long)blockIdx.y * bstride;
+  const T* yv = static_cast<const T*>(p.y_in) + (long long)blockIdx.y * bstride;
+  T* out = static_cast<T*>(p.out) + (long long)blockIdx.y * bstride;
+  const int br = row0 / p.BH, y0 = row0 - br * p.BH;
+  const int t0 = p.row_ptr[br], t1 = p.row_ptr[br + 1];
+  const int n = (t1 - t0) * p.BW;
+  const int shift = __ffs(p.BW) - 1;
+  const int nv = n / E;
+  const int row_bytes = nv * 16;
+  if (2 * row_bytes > kBwdRingBytes) {  // rows too long for the ring: scalar passes, row by row
+    for (int k = 0; k < rows_w; ++k) {
+      const int row = row0 + k * kRingWarps, y = y0 + k * kRingWarps;
+      float dot = 0.f;
+      for (int j = lane; j < n; j += 32) {
+        const long long o = elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1));
+        if (p.mask && !p.mask[o]) continue;
+        dot += to_float(dy[o]) * to_float(yv[o]);
+      }
+      dot = warp_sum(dot);
+      for (int j = lane; j < n; j += 32) {
+        const long long o = elem_off(p, t0 + (j >> shift), row, y, j & (p.BW - 1));
+        float r = 0.f;
+        if (!p.mask || p.mask[o]) {
+          const float yy = to_float(yv[o]);
+          r = (to_float(dy[o]) * yy - yy * dot) * p.scale;
+        }
+        out[o] = from_float<T>(r);
+      }
+    }
+    return;
+  }
+  const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(ring_smem)) + warp * kBwdRingBytes;
+  const uint8_t* ring_ptr = ring_smem + warp * kBwdRingBytes;
+  int slots = kBwdRingBytes / (2 * row_bytes);
+  if (slots > kRingMaxSlots) slots = kRingMaxSlots;
+  if (nv > 32 * kVecs) {
+    // rows longer than the registers hold (up to half the ring each): the same pipeline, two passes over the slot
+    const uint32_t step = p.compressed ? p.BW : p.W;
+    auto vec_off = [&](int v, int k) -> uint32_t {
+      const int j = v * E;
+      return static_cast<uint32_t>(elem_off(p, t0 + (j >> shift), row0, y0, j & (p.BW - 1))) + k * kRingWarps * step;
+    };
+    auto issue_long = [&](int k) {
+      if (k < rows_w) {
+        const uint32_t dst = ring + (k % slots) * (2 * row_bytes);
+        for (int v = lane; v < nv; v += 32) {
+          const uint32_t o = vec_off(v, k);
+          cp_async_16(dst + v * 16, dy + o);
+          cp_async_16(dst + row_bytes + v * 16, yv + o);
+        }
+      }
+      cp_async_commit();
+    };
+    for (int k = 0; k < slots - 1; ++k) issue_long(k);
+    for (int k = 0; k < rows_w; ++k) {
+      issue_long(k + slots - 1);
+      cp_async_wait_pending(slots - 1);
+      uint8_t* slot = const_cast<uint8_t*>(ring_ptr) + (k % slots) * (2 * row_bytes);
+      const uint4* gv = reinterpret_cast<const uint4*>(slot);
+      uint4* yvec = reinterpret_cast<uint4*>(slot + row_bytes);
+      float dot = 0.f;
+      for (int v = lane; v < nv; v += 32) {
+        const uint4 g = gv[v];
+        uint4 yy = yvec[v];
+        if (p.mask) {
+          const uint32_t o = vec_off(v, k);
+          unsigned long long mk;
+          if (E == 8) mk = *reinterpret_cast<const unsigned long long*>(p.mask + o);
+          else mk = *reinterpret_cast<const unsigned int*>(p.mask + o);
+          T* e = reinterpret_cast<T*>(&yy);
+#pragma unroll
+          for (int q = 0; q < E; ++q)
+            if (!((mk >> (8 * q)) & 0xffull)) e[q] = from_float<T>(0.f);
+          yvec[v] = yy;
+        }
+        const T* a = reinterpret_cast<const T*>(&g);
+        const T* b = reinterpret_cast<const T*>(&yy);
+#pragma unroll
+        for (int q = 0; q < E; ++q) dot = fmaf(to_float(a[q]), to_float(b[q]), dot);
+      }
+      dot = warp_sum(dot);
+      for (int v = lane; v < nv; v += 32) {
+        uint4 g = gv[v];
+        const uint4 yy = yvec[v];
+        T* a = reinterpret_cast<T*>(&g);
+        const T* b = reinterpret_cast<const T*>(&yy);
+#pragma unroll
+        for (int q = 0; q < E; ++q) {
+          const float yq = to_float(b[q]);
+          a[q] = from_float<T>((to_float(a[q]) * yq - yq * dot) * p.scale);
+        }
+        *reinterpret_cast<uint4*>(out + vec_off(v, k)) = g;
+      }
+    }
+    return;
+  }
+  if (n == 0) return;
+  uint32_t off0[kVecs];
+#pragma unroll
+  for (int i = 0; i < kVecs; ++i) {
+    const int j = (lane + 32 * i) * E;
+    off0[i] = j < n ? static_cast<uint32_t>(elem_off(p, t0 + (j >> shift), row0, y0, j & (p.BW - 1))) : 0u;
+  }
+  const uint32_t row_step = (p.compressed ? p.BW : p.W) * kRingWarps;
+
+  auto issue = [&](int k) {
+    if (k < rows_w) {
+      const uint32_t dst = ring + (k % slots) * (2 * row_bytes);
+#pragma unroll
+      for (int i = 0; i < kVecs; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nv) {
+          cp_async_16(dst + v * 16, dy + off0[i] + k * row_step);
+          cp_async_16(dst + row_bytes + v * 16, yv + off0[i] + k * row_step);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+  for (int k = 0; k < slots - 1; ++k) issue(k);
+  for (int k = 0; k < rows_w; ++k) {
+    issue(k + slots - 1);
+    cp_async_wait_pending(slots - 1);
+    const uint8_t* src = ring_ptr + (k % slots) * (2 * row_bytes);
+    uint4 g[kVecs], yy[kVecs];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kVecs; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nv) {
+        g[i] = *reinterpret_cast<const uint4*>(src + v * 16);
+        yy[i] = *reinterpret_cast<const uint4*>(src + row_bytes + v * 16);
+        if (p.mask) {
+          const uint32_t o = off0[i] + k * row_step;
+          unsigned long long mk;
+          if (E == 8) mk = *reinterpret_cast<const unsigned long long*>(p.mask + o);
+          else mk = *reinterpret_cast<const unsigned int*>(p.mask + o);
+          T* e = reinterpret_cast<T*>(&yy[i]);
+#pragma unroll
+          for (int q = 0; q < E; ++q)
+            if (!((mk >> (8 * q)) & 0xffull)) e[q] = from_float<T>(0.f);
+        }
+        const T* a = reinterpret_cast<const T*>(&g[i]);
+        const T* b = reinterpret_cast<const T*>(&yy[i]);
+#pragma unroll
+        for (int q = 0; q < E; ++q) dot = fmaf(to_float(a[q]), to_float(b[q]), dot);
+      }
+    }
+    dot = warp_sum(dot);
+#pragma unroll
+    for (int i = 0; i < kVecs; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nv) {
+        T* a = reinterpret_cast<T*>(&g[i]);
+        const T* b = reinterpret_cast<const T*>(&yy[i]);
+#pragma unroll
+        for (int q = 0; q < E; ++q) {
+          const float yq = to_float(b[q]);
+          a[q] = from_float<T>((to_float(a[q]) * yq - yq * dot) * p.scale);
+        }
+        *reinterpret_cast<uint4*>(out + off0[i] + k * row_step) = g[i];
+      }
+    }
+  }
+}
+
 // whether the 16-byte path applies: block width and row pitch multiples of the vector, aligned bases
 bool vec_ok(const SmParams& p, int dtype) {
   const int esz = dtype == SPARTA_F32 ? 4 : 2, E = 16 / esz;
   if (p.BW % E || !(p.scale > 0.f)) return false;  // the kernel scales the row maximum after taking it
-  if ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.out)) & 15) return false;
+  if ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.y_in)) & 15) return false;
   if (p.mask && (reinterpret_cast<uintptr_t>(p.mask) & 7)) return false;
   const long long bstride = p.compressed ? p.val_stride_blocks * p.BH * p.BW : (long long)p.H * p.W;
   if (bstride % E || bstride >= (1ll << 32)) return false;
@@ -484,6 +667,28 @@ int launch(const SmParams& p, int batch, int dtype, cudaStream_t st) {
       case SPARTA_BF16:
         if (cudaError_t e = attr_b.ensure(softmax_fwd_ring_kernel<__nv_bfloat16>, kSmem); e != cudaSuccess) return (int)e;
         softmax_fwd_ring_kernel<__nv_bfloat16><<<grid, block, kSmem, st>>>(p);
+        break;
+      default: return SPARTA_ERR_BAD_ARG;
+    }
+    return launch_status();
+  }
+  if (BACKWARD && vec_ok(p, dtype) && p.BH >= 4 * kRingWarps) {
+    const int rows_cta = kRingWarps * (kRingRows < p.BH / kRingWarps ? kRingRows : p.BH / kRingWarps);
+    const dim3 grid(p.H / rows_cta, batch), block(kRingWarps * 32);
+    constexpr int kSmem = kRingWarps * kBwdRingBytes;
+    static SmemAttrOnce attr_f, attr_h, attr_b;
+    switch (dtype) {
+      case SPARTA_F32:
+        if (cudaError_t e = attr_f.ensure(softmax_bwd_ring_kernel<float>, kSmem); e != cudaSuccess) return (int)e;
+        softmax_bwd_ring_kernel<float><<<grid, block, kSmem, st>>>(p);
+        break;
+      case SPARTA_F16:
+        if (cudaError_t e = attr_h.ensure(softmax_bwd_ring_kernel<__half>, kSmem); e != cudaSuccess) return (int)e;
+        softmax_bwd_ring_kernel<__half><<<grid, block, kSmem, st>>>(p);
+        break;
+      case SPARTA_BF16:
+        if (cudaError_t e = attr_b.ensure(softmax_bwd_ring_kernel<__nv_bfloat16>, kSmem); e != cudaSuccess) return (int)e;
+        softmax_bwd_ring_kernel<__nv_bfloat16><<<grid, block, kSmem, st>>>(p);
         break;
       default: return SPARTA_ERR_BAD_ARG;
     }

@@ -144,10 +144,11 @@ def test_half_types_element_mask(dtype, compressed):
 @pytest.mark.parametrize('dtype,W', [(torch.float16, 8192), (torch.bfloat16, 8192), (torch.float32, 4096)])
 @pytest.mark.parametrize('compressed', [True, False])
 @pytest.mark.parametrize('element_mask', [False, True])
-def test_row_lengths_across_the_forward_paths(dtype, W, compressed, element_mask):
+def test_row_lengths_across_the_kernel_paths(dtype, W, compressed, element_mask):
     """Block rows of very different lengths in one launch: a row that fits the registers (<= 4 KB of kept
     values), one that is processed in the shared-memory ring (<= 8 KB), one longer than the ring (scalar
-    passes), and an empty one; 64-row blocks (eight rows per warp) and 16-row blocks (four)."""
+    passes), and an empty one; 64-row blocks (eight rows per warp) and 16-row blocks (four).  The backward
+    pass goes through its own ring (dy and y rows side by side) or scalar passes for the long rows."""
     esz = 4 if dtype == torch.float32 else 2
     g = torch.Generator().manual_seed(W + esz)
     for bh in (64, 16):
@@ -161,13 +162,18 @@ def test_row_lengths_across_the_forward_paths(dtype, W, compressed, element_mask
         if element_mask:
             mask = mask * (torch.rand((H, W), generator=g) > 0.3).to(torch.uint8)
             mask[bh + 3] = 0  # a fully masked row inside kept blocks
+        grad = torch.randn((2, H, W), generator=g).to(dtype)
         op = SparseSoftmax(mask.cuda(), 3.0, compressed=compressed)
-        op.build({'forward:y': params(bh, 64)}, sample_inputs=[x.cuda()])
+        op.build({'forward:y': params(bh, 64), 'backward:x': params(bh, 64)}, sample_inputs=[x.cuda()])
         ix = op.get_sparse_indexes('y')
-        xin = ix.convert(x.cuda()) if compressed else x.cuda()
+        xin = (ix.convert(x.cuda()) if compressed else x.cuda()).requires_grad_()
         out = op(xin)
-        got = ix.inverse(out) if compressed else out
+        out.backward(ix.convert(grad.cuda()) if compressed else grad.cuda())
+        got = ix.inverse(out.detach()) if compressed else out.detach()
+        got_dx = ix.inverse(xin.grad) if compressed else xin.grad
         want = oracle.softmax_forward_reference(x.float(), mask, 3.0)
+        want_dx = oracle.softmax_backward_reference(grad.float(), want, mask, 3.0)
         tol = TOL if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
         torch.testing.assert_close(got.float().cpu(), want, **tol)
-        assert torch.all(got[:, 3 * bh:] == 0)
+        torch.testing.assert_close(got_dx.float().cpu(), want_dx, **tol)
+        assert torch.all(got[:, 3 * bh:] == 0) and torch.all(got_dx[:, 3 * bh:] == 0)
