@@ -743,7 +743,15 @@ def main():
     def e2e_step():
         streamed(x_host, y_host)
 
-    e2e_step()
+    e2e_how = 'the sequence replayed from a CUDA graph'
+    try:
+        e2e_step()
+        e2e_step()  # the first call ran plainly once, captured and replayed; this one replays
+    except Exception:  # capture refused on this box: plain launches
+        torch.cuda.synchronize()
+        streamed = sparta.nn.HostStreamedRows(chunk['op'], E2E_CHUNK)
+        e2e_how = 'plain launches (graph capture failed)'
+        e2e_step()
     torch.cuda.synchronize()
     if not torch.allclose(y_host.float(), wl['fn']().float().cpu(), rtol=2e-2, atol=2e-2):
         raise RuntimeError('end-to-end result differs from the device-resident result')
@@ -799,7 +807,7 @@ def main():
             'e2e': {'value': e2e_value, 'unit': 'TFLOP/s', 'ms_per_step': e2e_ms / args.steps,
                     'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': d2h_bytes,
                     'how': f'SparseLinear built for {E2E_CHUNK} rows, called through sparta.nn.HostStreamedRows: '
-                           f'{TOKENS // E2E_CHUNK} chunks, copy-in / kernel / copy-out overlapped on three streams, the sequence replayed from a CUDA graph'},
+                           f'{TOKENS // E2E_CHUNK} chunks, copy-in / kernel / copy-out overlapped on three streams, ' + e2e_how},
             'gpu_launches': args.steps,
             'clocks': clocks,
             'ranks': ranks,

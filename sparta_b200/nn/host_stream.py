@@ -21,7 +21,9 @@ class HostStreamedRows(object):
         graph: capture the whole sequence (copies, kernels and their cross-stream dependencies) in a CUDA
             graph on the first call for a pair of host buffers and replay it afterwards: one launch instead
             of about a dozen host calls per chunk.  The host buffers' addresses are baked into the graph, so
-            a different buffer (or shape) captures anew; a capture that fails falls back to plain launches.
+            a different buffer (or shape) captures anew.  The operator must be capturable: no synchronisation
+            and no host-side read of device data inside it (the prebuilt kernels of this package qualify; a
+            failed capture raises, and PyTorch leaves the CUDA random generator unusable after one).
 
     ``__call__(x_host, y_host)`` enqueues everything relative to the current stream: work starts after
     what the current stream already holds and the current stream waits for the last copy out, so events
@@ -61,13 +63,10 @@ class HostStreamedRows(object):
             self._enqueue(x_host, y_host, device)  # plain first pass: buffers, lazy initialisation in the operator
             torch.cuda.synchronize(device)
             graph = torch.cuda.CUDAGraph()
-            try:
-                with torch.cuda.graph(graph):
-                    self._enqueue(x_host, y_host, device)
-            except Exception:  # e.g. an operator that synchronises or allocates outside the graph's pool
-                self._use_graph = False
-                torch.cuda.synchronize(device)
-                return self._enqueue(x_host, y_host, device)
+            # thread-local capture mode: other threads of the process (a collective library's watchdog) may go on
+            # making CUDA calls while this thread captures
+            with torch.cuda.graph(graph, capture_error_mode='thread_local'):
+                self._enqueue(x_host, y_host, device)
             self._graph, self._graph_key = graph, key
         self._graph.replay()
         return y_host

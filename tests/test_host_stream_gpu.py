@@ -36,8 +36,7 @@ def test_streamed_rows_match_single_call(chunks, depth):
 
 
 def test_streamed_rows_replayed_from_a_graph():
-    """graph=True: the second and later calls replay the captured sequence; new host buffers capture anew;
-    an operator that cannot be captured (it synchronises) falls back to plain launches."""
+    """graph=True: the second and later calls replay the captured sequence; new host buffers capture anew."""
     rows, K, N, chunks = 1024, 256, 384, 4
     g = torch.Generator().manual_seed(8)
     mask = oracle.block_mask((N, K), (32, 32), 0.6, generator=g).cuda()
@@ -55,17 +54,6 @@ def test_streamed_rows_replayed_from_a_graph():
             torch.cuda.synchronize()
             assert torch.equal(y_host, whole_op(x_host.cuda()).cpu())
         assert streamed._graph is not None
-
-    def syncing_op(t):
-        torch.cuda.synchronize()
-        return t * 2
-    fallback = sparta.nn.HostStreamedRows(syncing_op, 256, graph=True)
-    x_host, y_host = torch.ones((512, 8)).pin_memory(), torch.empty((512, 8)).pin_memory()
-    for _ in range(2):
-        fallback(x_host, y_host)
-        torch.cuda.synchronize()
-        assert torch.all(y_host == 2)
-    assert fallback._graph is None
 
 
 def test_streamed_rows_rejects_bad_inputs():
