@@ -80,7 +80,9 @@ __global__ void __launch_bounds__(2 * TM) bsmm_dsd_fma_kernel(BsmmParams p) {
   extern __shared__ __align__(16) uint8_t stage_mem[];
   __shared__ uint32_t kmask[kMaxKbFma];
   __shared__ uint16_t wpos[kMaxKbFma * P];
+  __shared__ uint16_t clist[kMaxKbFma * B / kChunkK + 1];  // chunks of K in which the panel keeps a block, ascending
   __shared__ int s_range[2];
+  __shared__ int s_nchunks;
 
   const int panel = blockIdx.x, m0 = blockIdx.y * TM, batch = blockIdx.z;
   const int Nb = p.N / B, Kb = p.K / B;
@@ -103,9 +105,27 @@ __global__ void __launch_bounds__(2 * TM) bsmm_dsd_fma_kernel(BsmmParams p) {
   }
   __syncthreads();
 
+  // Only the chunks of K in which this panel keeps a block are fetched and walked: with few blocks left, reading
+  // every activation chunk for every panel was most of the time (and all of it for a panel without blocks).
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x, all = p.K / kChunkK;
+    int n = 0;
+    for (int c0 = 0; c0 < all; c0 += 32) {
+      const int c = c0 + lane;
+      uint32_t any = 0;
+      if (c < all)
+        for (int kc = 0; kc < KC; ++kc) any |= kmask[c * KC + kc];
+      const unsigned bal = __ballot_sync(0xffffffffu, any != 0);
+      if (any) clist[n + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>(c);
+      n += __popc(bal);
+    }
+    if (lane == 0) s_nchunks = n;
+  }
+  __syncthreads();
+
   const T* xtile = static_cast<const T*>(p.A) + ((long long)batch * p.M + m0) * p.K;
   const T* wbase = static_cast<const T*>(p.B) + ((long long)batch * p.val_stride_blocks + e0) * (B * B);
-  const int n_chunks = p.K / kChunkK;
+  const int n_chunks = s_nchunks;
 
   // staging: every thread copies the same 16-byte piece of successive rows / block slots, so the
   // index arithmetic is done once
@@ -116,7 +136,8 @@ __global__ void __launch_bounds__(2 * TM) bsmm_dsd_fma_kernel(BsmmParams p) {
   const int x_r0 = threadIdx.x / XP, x_q = threadIdx.x % XP;
   const uint8_t* x_src0 = reinterpret_cast<const uint8_t*>(xtile + (long long)x_r0 * p.K) + x_q * 16;
   const long long x_step = (long long)(NT / XP) * p.K * (long long)sizeof(T);
-  auto issue = [&](int c, int buf) {
+  auto issue = [&](int ci, int buf) {  // ci: position in clist
+    const int c = clist[ci];
     uint8_t* xs = stage_mem + buf * S::kStage;
     uint8_t* ws = xs + S::kXBytes;
     const uint8_t* src = x_src0 + (long long)c * kChunkK * sizeof(T);
@@ -157,9 +178,10 @@ __global__ void __launch_bounds__(2 * TM) bsmm_dsd_fma_kernel(BsmmParams p) {
     const uint8_t* xs = stage_mem + (c % S::kStages) * S::kStage;
     const uint8_t* ws = xs + S::kXBytes;
     const T* xrow = reinterpret_cast<const T*>(xs + (threadIdx.x % TM) * S::kXRow);
+    const int chunk = clist[c];
 #pragma unroll 1
     for (int kc = threadIdx.x / TM; kc < KC; kc += 2) {  // the two threads of a row take alternate K-blocks
-      const uint32_t m = kmask[c * KC + kc];  // the same for every thread of the CTA
+      const uint32_t m = kmask[chunk * KC + kc];  // the same for every thread of the CTA
       if (!m) continue;
       float x[B];
       load_floats<T, B>(xrow + kc * B, x);
@@ -167,14 +189,28 @@ __global__ void __launch_bounds__(2 * TM) bsmm_dsd_fma_kernel(BsmmParams p) {
       for (int l = 0; l < P; ++l) {
         if (!((m >> l) & 1u)) continue;
         const T* wb = reinterpret_cast<const T*>(ws) + (kc * P + l) * (B * B);  // stored [n][k], row-major
+        // four outputs at a time: their multiply-add chains are independent, so one is always ready to issue
+        // (a single chain of B dependent multiply-adds per output left the FMA pipe waiting on its own latency)
+        constexpr int KV = 16 / (int)sizeof(T);  // values per 16-byte vector
 #pragma unroll
-        for (int n = 0; n < B; ++n) {
-          float w[B];
-          load_floats<T, B>(wb + n * B, w);
-          float s = acc[l * B + n];
+        for (int n = 0; n < B; n += 4) {
+          float s0 = acc[l * B + n], s1 = acc[l * B + n + 1], s2 = acc[l * B + n + 2], s3 = acc[l * B + n + 3];
 #pragma unroll
-          for (int kk = 0; kk < B; ++kk) s = fmaf(x[kk], w[kk], s);
-          acc[l * B + n] = s;
+          for (int k0 = 0; k0 < B; k0 += KV) {
+            float w0[KV], w1[KV], w2[KV], w3[KV];
+            load_floats<T, KV>(wb + (n + 0) * B + k0, w0);
+            load_floats<T, KV>(wb + (n + 1) * B + k0, w1);
+            load_floats<T, KV>(wb + (n + 2) * B + k0, w2);
+            load_floats<T, KV>(wb + (n + 3) * B + k0, w3);
+#pragma unroll
+            for (int kk = 0; kk < KV; ++kk) {
+              s0 = fmaf(x[k0 + kk], w0[kk], s0);
+              s1 = fmaf(x[k0 + kk], w1[kk], s1);
+              s2 = fmaf(x[k0 + kk], w2[kk], s2);
+              s3 = fmaf(x[k0 + kk], w3[kk], s3);
+            }
+          }
+          acc[l * B + n] = s0; acc[l * B + n + 1] = s1; acc[l * B + n + 2] = s2; acc[l * B + n + 3] = s3;
         }
       }
     }
