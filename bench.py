@@ -300,6 +300,61 @@ def refgrid_extras(device, timed):
     return rows
 
 
+def refgrid_attention_extras(device, timed):
+    """Forward and backward latency over the grid of the reference's attention benchmark
+    (test/bench/attention/attention.py:18-23: one head, Ns 4096, Nt 3072, E 768, uniform [0, 1) inputs, mask
+    granularity 1 / 8 / 32; five of its twelve sparsities), in microseconds: the masked dense softmax attention in
+    torch (fp32), this library's three-operator SparseAttention in fp32 (FMA kernels, 32 x 32 tiles) and in fp16 with
+    every matmul on a tcgen05 tile.  E = 768 is outside the fused kernel (64 / 128), as in the reference."""
+    import sparta_b200 as sparta
+    from oracle import oracle
+    Ns, Nt, E = 4096, 3072, 768
+    mm = lambda m, k, n, fam: {'_impl': 'sparta', '_family': fam, 'BLOCK_SIZE_M_VALUE': m, 'BLOCK_SIZE_K_VALUE': k,
+                               'BLOCK_SIZE_N_VALUE': n}
+    sm = {'_impl': 'sparta', 'BLOCK_SIZE_H_VALUE': 32, 'BLOCK_SIZE_W_VALUE': 32, 'ROW_TILE_VALUE': 4}
+    slots = ['qk/forward:C', 'qk/backward:A', 'qk/backward:B', 'out/forward:C', 'out/backward:A', 'out/backward:B']
+    fma_cfg = {**{n: mm(32, 32, 32, 'simt') for n in slots}, 'sm/forward:y': sm, 'sm/backward:x': sm}
+    dds, sdd = mm(32, 64, 32, 'tcgen05'), mm(32, 32, 128, 'tcgen05')
+    tc_cfg = {'qk/forward:C': dds, 'qk/backward:A': sdd, 'qk/backward:B': sdd, 'out/forward:C': sdd,
+              'out/backward:A': dds, 'out/backward:B': sdd, 'sm/forward:y': sm, 'sm/backward:x': sm}
+    rows = []
+    for gran in (1, 8, 32):
+        for sp in (0, 0.6, 0.9, 0.99, 0.999):
+            g = torch.Generator().manual_seed(2022)
+            q = torch.rand((1, Nt, E), generator=g)
+            k, v = torch.rand((1, Ns, E), generator=g), torch.rand((1, Ns, E), generator=g)
+            go = torch.rand((1, Nt, E), generator=g)
+            mask = oracle.block_mask((Nt, Ns), (gran, gran), sp, generator=g)
+            if int(mask.sum()) == 0:
+                continue
+            md = mask.to(device)
+            row = {'granularity': gran, 'sparsity': sp}
+
+            def fwd_bwd(fn, q_, k_, v_, go_):
+                q_.grad = k_.grad = v_.grad = None
+                fn(q_, k_, v_).backward(go_)
+
+            def dense(q_, k_, v_):
+                s_ = torch.matmul(q_, k_.transpose(1, 2)) / (E ** 0.5)
+                s_ = s_.masked_fill(md == 0, float('-inf'))
+                p_ = torch.nan_to_num(torch.softmax(s_, dim=-1))
+                return torch.matmul(p_, v_)
+            legs = [('dense_fp32', dense, torch.float32, None), ('ours_fp32', None, torch.float32, fma_cfg),
+                    ('ours_fp16_tcgen05', None, torch.float16, tc_cfg)]
+            for name, fn, dtype, cfg in legs:
+                qd, kd, vd = (t.to(device=device, dtype=dtype).requires_grad_() for t in (q, k, v))
+                gd = go.to(device=device, dtype=dtype)
+                if fn is None:
+                    op = sparta.nn.SparseAttention(mask=md, fused=False)
+                    op.build(cfg, sample_inputs=[qd, kd, vd])
+                    fn = op
+                with torch.no_grad():
+                    row[name + '_fwd_us'] = round(timed(lambda: fn(qd, kd, vd), steps=5) * 1e3, 1)
+                row[name + '_fwd_bwd_us'] = round(timed(lambda: fwd_bwd(fn, qd, kd, vd, gd), steps=5) * 1e3, 1)
+            rows.append(row)
+    return rows
+
+
 def run_extras(device, peaks, flush, only=None):
     """Secondary measurements (each: 3 warm-ups, 10 timed steps, L2 flushed between steps)."""
     import sparta_b200 as sparta
@@ -549,6 +604,12 @@ def run_extras(device, peaks, flush, only=None):
         extras['refgrid'] = refgrid_extras(device, timed)
     except Exception as e:
         extras['refgrid'] = {'error': repr(e)[:200]}
+    try:
+        if only is None or 'refgrid_attention' not in only:
+            raise KeyError('skipped')
+        extras['refgrid_attention'] = refgrid_attention_extras(device, timed)
+    except Exception as e:
+        extras['refgrid_attention'] = {'error': repr(e)[:200]}
     return {k: v for k, v in extras.items() if not (isinstance(v, dict) and 'skipped' in str(v.get('error', '')))}
 
 
@@ -677,7 +738,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-extras', action='store_true')
     ap.add_argument('--extras', default=None,
-                    help='comma list of extra measurements to run: linear,linear_train,dense,attention,attention_d128,attention_c5,softmax,convert,readme,ref_gpu (default: all of these), refgrid (only when named)')
+                    help='comma list of extra measurements to run: linear,linear_train,dense,attention,attention_d128,attention_c5,softmax,convert,readme,ref_gpu (default: all of these), refgrid and refgrid_attention (only when named)')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
 

@@ -87,7 +87,11 @@ class SparseMatMulKernel(KernelBase):
         code = _lib.DTYPE_CODE[self._sample_dtype if dtype is None else dtype]
         shapes: Dict[Any, int] = {}
         for e in _lib.tile_table(_OP_CODE[self._mode], code):
-            if e.trans_a not in (-1, int(self._transpose_A)) or e.trans_b not in (-1, int(self._transpose_B)):
+            # sdd against a dense B stored [K, N] reaches the tcgen05 kernel (which wants B stored [N, K])
+            # through a transposed copy of B made by the launch closure, see update_func
+            b_ok = e.trans_b in (-1, int(self._transpose_B)) or \
+                (self._mode == 'sdd' and e.impl == _lib.IMPL_TCGEN05 and e.trans_b == 1)
+            if e.trans_a not in (-1, int(self._transpose_A)) or not b_ok:
                 continue
             if e.compressed not in (-1, int(self._compressed)):
                 continue
@@ -146,6 +150,8 @@ class SparseMatMulKernel(KernelBase):
         entry = getattr(_lib.lib(), _ENTRY[mode])
         impl = _FAMILY[self._family]
         by_row = self._bcs_mode == 'BCSR'
+        via_transposed_b = (mode == 'sdd' and not trans_b and compressed and (BM, BK, BN) == (32, 32, 128)
+                            and self._family != 'simt')
 
         cache = {}
 
@@ -156,6 +162,12 @@ class SparseMatMulKernel(KernelBase):
             assert A.dtype == B.dtype, 'A and B must share a dtype'
             A = A.contiguous()
             B = B.contiguous()
+            # sdd with B stored [K, N] on a tcgen05 tile: the kernel reads its dense operand with the reduction
+            # dimension contiguous, so B is transposed first -- one extra pass over B (in attention: over V,
+            # which is small beside the probabilities); the FMA kernels take B as it is
+            b_transposed = via_transposed_b and A.dtype in (torch.float16, torch.bfloat16)
+            if b_transposed:
+                B = B.transpose(1, 2).contiguous()
             batch = A.shape[0]
             stride = idx.val_stride_blocks
             if mode == 'dds' and compressed:
@@ -176,7 +188,7 @@ class SparseMatMulKernel(KernelBase):
                 args = _lib.BsmmArgs(
                     ptr=ptr_t.data_ptr(), idx=idx_t.data_ptr(), nnz=idx.nnz_dev.data_ptr(),
                     batch=batch, M=M, K=K, N=N, BM=BM, BK=BK, BN=BN,
-                    trans_a=int(trans_a), trans_b=int(trans_b), compressed=int(compressed),
+                    trans_a=int(trans_a), trans_b=int(trans_b or b_transposed), compressed=int(compressed),
                     idx_is_64=int(is64), dtype=_lib.dtype_code(A), impl=impl,
                     n_index_sets=idx.n_masks if idx.batched else 1,
                     ptr_stride=ptr_t.shape[-1], idx_stride=idx.capacity,

@@ -206,3 +206,43 @@ def test_fused_attention_with_copies_of_the_output(dtype):
     buf = torch.empty((2, 1, 256, 64), dtype=dtype, device='cuda')
     with pytest.raises(_lib.SpartaError):
         op.forward_gathered(q.cuda(), k.cuda(), v.cuda(), buf[0], [buf[1].data_ptr()])
+
+
+def tc_params():
+    """Every matmul of the three-operator attention on a tcgen05 tile (32 x 32 sparse blocks): the two dds products
+    on 32 x 64 x 32, the four sdd products (stored [K, N] dense operands included) on 32 x 32 x 128."""
+    tc = {'_impl': 'sparta', '_family': 'tcgen05'}
+    dds = {**tc, 'BLOCK_SIZE_M_VALUE': 32, 'BLOCK_SIZE_K_VALUE': 64, 'BLOCK_SIZE_N_VALUE': 32}
+    sdd = {**tc, 'BLOCK_SIZE_M_VALUE': 32, 'BLOCK_SIZE_K_VALUE': 32, 'BLOCK_SIZE_N_VALUE': 128}
+    sm = {'_impl': 'sparta', 'BLOCK_SIZE_H_VALUE': 32, 'BLOCK_SIZE_W_VALUE': 32, 'ROW_TILE_VALUE': 4}
+    return {'qk/forward:C': dds, 'qk/backward:A': sdd, 'qk/backward:B': sdd,
+            'out/forward:C': sdd, 'out/backward:A': dds, 'out/backward:B': sdd,
+            'sm/forward:y': sm, 'sm/backward:x': sm}
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_three_operator_attention_trains_on_tcgen05(dtype):
+    """Forward and q / k / v gradients of the composed attention with all six matmuls pinned to the tcgen05 kernels
+    (a head dimension of 256 keeps the fused kernel out), against oracle autograd."""
+    from sparta_b200 import _lib
+    heads, Nt, Ns, E = 2, 256, 384, 256
+    g = torch.Generator().manual_seed(14)
+    q = torch.randn((heads, Nt, E), generator=g).to(dtype)
+    k, v = (torch.randn((heads, Ns, E), generator=g).to(dtype) for _ in range(2))
+    grad = torch.randn((heads, Nt, E), generator=g).to(dtype)
+    mask = oracle.block_mask((Nt, Ns), (32, 32), 0.6, generator=g)
+    mask[64:96] = 0
+    op = SparseAttention(mask=mask.cuda())
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    op.build(config=tc_params(), sample_inputs=[qc, kc, vc])
+    assert not op._use_fused
+    out = op(qc, kc, vc)
+    out.backward(grad.cuda())
+    assert _lib.last_status() == [0, 0, 0, 0]
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    target = oracle.attention_reference(qr, kr, vr, mask)
+    target.backward(grad.float())
+    tol = dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(out.detach().float().cpu(), target.detach(), **tol)
+    for got, want in ((qc.grad, qr.grad), (kc.grad, kr.grad), (vc.grad, vr.grad)):
+        torch.testing.assert_close(got.float().cpu(), want, **tol)

@@ -130,11 +130,12 @@ def test_search_space_follows_the_tile_table():
     assert bwd.tile_shapes(torch.float16)[(128, 32, 32)] == _lib.IMPL_TCGEN05
     bwd = op.get_kernel_placeholders(True)['backward:B'].possible_kernels['sparta']
     assert bwd.tile_shapes(torch.float16)[(32, 64, 32)] == _lib.IMPL_TCGEN05
-    # sdd: only against a dense B stored [N, K]
+    # sdd: against a dense B stored [N, K], and (through a transposed copy made by the launch closure) [K, N]
     from sparta_b200.specializer.kernels import SparTASparseMatMulKernel
     sdd = lambda tb: SparTASparseMatMulKernel(mode='sdd', biased=False, transpose_A=False, transpose_B=tb)
     assert sdd(True).tile_shapes(torch.float16)[(32, 32, 128)] == _lib.IMPL_TCGEN05
-    assert all(impl == _lib.IMPL_SIMT for impl in sdd(False).tile_shapes(torch.float16).values())
+    assert sdd(False).tile_shapes(torch.float16)[(32, 32, 128)] == _lib.IMPL_TCGEN05
+    assert all(impl == _lib.IMPL_SIMT for impl in sdd(False).tile_shapes(torch.float32).values())
 
 
 def test_grid_and_random_walkers():

@@ -203,11 +203,13 @@ def test_dsd_nn_tcgen05(dtype, both_forms, batch, M, K, N, sparsity):
     (1, 544, 2048, 384, 0.75, True),
     (2, 384, 4096, 256, 0.97, True),
 ])
-def test_sdd_tcgen05(dtype, trans_A, both_forms, batch, M, K, N, sparsity, biased):
-    """sdd against a dense B stored [N, K] runs as C^T = B A^T on the dsd kernel with a transposed store."""
+@pytest.mark.parametrize('trans_B', [True, False])
+def test_sdd_tcgen05(dtype, trans_A, both_forms, batch, M, K, N, sparsity, biased, trans_B):
+    """sdd against a dense B stored [N, K] runs as C^T = B A^T on the dsd kernel with a transposed store; a B
+    stored [K, N] (the P V product of attention) gets there through a transposed copy."""
     g = torch.Generator().manual_seed(M + K + N + 2)
     a = (torch.randn((batch, K, M) if trans_A else (batch, M, K), generator=g) * 0.1).to(dtype)
-    b = torch.randn((batch, N, K), generator=g).to(dtype)
+    b = torch.randn((batch, N, K) if trans_B else (batch, K, N), generator=g).to(dtype)
     bias = torch.randn((batch, N), generator=g).to(dtype) if biased else None
     mask = oracle.block_mask((K, M) if trans_A else (M, K), (32, 32), sparsity, generator=g)
     if M >= 192:
@@ -216,7 +218,7 @@ def test_sdd_tcgen05(dtype, trans_A, both_forms, batch, M, K, N, sparsity, biase
         else:
             mask[32:64] = 0  # a block row of A without any block: those rows of C are bias only
     a = a * mask
-    kernel = SparTASparseMatMulKernel(mode='sdd', biased=biased, transpose_A=trans_A, transpose_B=True,
+    kernel = SparTASparseMatMulKernel(mode='sdd', biased=biased, transpose_A=trans_A, transpose_B=trans_B,
                                       compressed=True)
     if both_forms:
         kernel.ports['A'].set_sparse(True, True)
@@ -228,7 +230,7 @@ def test_sdd_tcgen05(dtype, trans_A, both_forms, batch, M, K, N, sparsity, biase
     args = [ix.convert(a.cuda()), b.cuda()] + ([bias.cuda()] if biased else [])
     out, ref = _run_both_families(kernel, {**cfg, 'BLOCK_SIZE_N_VALUE': 128}, {**cfg, 'BLOCK_SIZE_N_VALUE': 64}, args)
     expect = oracle.matmul_reference(a.float(), b.float(), bias.float() if biased else None, mask, 'sdd',
-                                     trans_A, True, (32, 32))
+                                     trans_A, trans_B, (32, 32))
     torch.testing.assert_close(out.float().cpu(), expect, **TOL)
     torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
 
