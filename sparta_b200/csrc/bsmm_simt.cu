@@ -6,13 +6,19 @@
 // Replaces sparta_sparse_matmul_{sdd,dsd,dds}.cuh.j2 and openai_sparse_matmul_{sdd,dsd,dds}.cuh.j2
 // (sparta/specializer/kernels/templates/).  As in the reference the CTA tile (BM, BK, BN) equals the
 // block size of the sparse operand in its two dimensions (sparta/specializer/kernels/matmul.py:53-97).
+#include <cstring>
+
 #include "bsmm.cuh"
 
 namespace sparta {
 namespace {
 
-constexpr int kThreads = 256;
 constexpr int kMaxTile = 64;
+// A thread computes R x R outputs (R = 4, 2 or 1, chosen so that a CTA has at least 64 threads where the tile
+// allows it: a 32 x 32 tile is 64 threads of 4 x 4, a 64 x 64 tile 256 threads); its R rows and R columns are
+// contiguous, so that one vector read of shared memory fetches them: 2 reads per 16 multiply-adds for R = 4.
+// (A fixed 16 x 16 grid of threads with 4 x 4 outputs each, as before, spent three quarters of its multiply-adds
+// on padding for 32 x 32 tiles.)  Shared memory is sized by the tile, so small tiles put many CTAs on an SM.
 
 struct Operand {   // where the current K-chunk of an operand tile lives
   const void* base;
@@ -20,31 +26,97 @@ struct Operand {   // where the current K-chunk of an operand tile lives
   long long s_k;      // stride along K
 };
 
+// four consecutive elements as fp32 (16-byte aligned for fp32, 8-byte for the 16-bit types)
 template <typename T>
-__device__ __forceinline__ void stage_tile(float* smem, const Operand& op, int outer, int tk, int ld) {
-  // smem[kk * ld + o] = tile(o, kk); consecutive threads follow the unit-stride dimension
+__device__ __forceinline__ float4 load4(const T* src) {
+  if constexpr (sizeof(T) == 4) {
+    return *reinterpret_cast<const float4*>(src);
+  } else {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    T e[4];
+    memcpy(e, &raw, 8);
+    return make_float4(to_float(e[0]), to_float(e[1]), to_float(e[2]), to_float(e[3]));
+  }
+}
+
+// smem[kk * ld + o] = tile(o, kk) for an outer x tk tile (sizes are powers of two >= 4).  With `vec` (aligned
+// operand) a thread moves four elements of the operand's unit-stride dimension at a time and has four such loads
+// in flight before it stores the first: a CTA may be as small as 64 threads, and one scalar load per loop turn
+// left a lone CTA (a nearly empty mask) waiting out the memory latency sixteen times per tile.
+template <typename T>
+__device__ __forceinline__ void stage_tile(float* smem, const Operand& op, int outer, int tk, int ld, int outer_shift,
+                                           int tk_shift, bool vec) {
   const T* g = static_cast<const T*>(op.base);
   const int total = outer * tk;
+  const int nt = blockDim.x;
+  if (vec) {
+    const int nvec = total >> 2;
+    const bool k_unit = op.s_k == 1;  // else the outer dimension has unit stride
+    const int vshift = (k_unit ? tk_shift : outer_shift) - 2, vmask = (1 << vshift) - 1;
+    const long long line_stride = k_unit ? op.s_outer : op.s_k;
+    for (int i0 = threadIdx.x; i0 < nvec; i0 += 4 * nt) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * nt;
+        if (i < nvec) v[u] = load4<T>(g + (long long)(i >> vshift) * line_stride + ((i & vmask) << 2));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * nt;
+        if (i < nvec) {
+          const int line = i >> vshift, q = (i & vmask) << 2;
+          if (k_unit) {  // line = o, q = first of four kk
+            float* d = smem + q * ld + line;
+            d[0] = v[u].x; d[ld] = v[u].y; d[2 * ld] = v[u].z; d[3 * ld] = v[u].w;
+          } else {       // line = kk, q = first of four o
+            *reinterpret_cast<float4*>(smem + line * ld + q) = v[u];
+          }
+        }
+      }
+    }
+    return;
+  }
   if (op.s_k == 1) {
-    for (int i = threadIdx.x; i < total; i += kThreads) {
-      const int o = i / tk, kk = i - o * tk;
+    for (int i = threadIdx.x; i < total; i += nt) {
+      const int o = i >> tk_shift, kk = i & (tk - 1);
       smem[kk * ld + o] = to_float(g[(long long)o * op.s_outer + kk]);
     }
   } else {
-    for (int i = threadIdx.x; i < total; i += kThreads) {
-      const int kk = i / outer, o = i - kk * outer;
+    for (int i = threadIdx.x; i < total; i += nt) {
+      const int kk = i >> outer_shift, o = i & (outer - 1);
       smem[kk * ld + o] = to_float(g[(long long)o * op.s_outer + (long long)kk * op.s_k]);
     }
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kThreads) bsmm_simt_kernel(BsmmParams p) {
-  __shared__ float As[kMaxTile * (kMaxTile + 1)];
-  __shared__ float Bs[kMaxTile * (kMaxTile + 1)];
+template <int R>
+__device__ __forceinline__ void load_frag(const float* src, float (&out)[R]) {  // R contiguous floats, R * 4-byte aligned
+  if constexpr (R == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(src);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+  } else if constexpr (R == 2) {
+    const float2 v = *reinterpret_cast<const float2*>(src);
+    out[0] = v.x; out[1] = v.y;
+  } else {
+    out[0] = src[0];
+  }
+}
+
+template <typename T, int R>
+__global__ void __launch_bounds__(256) bsmm_simt_kernel(BsmmParams p) {
+  extern __shared__ __align__(16) float simt_smem[];
   const int tm = p.BM, tn = p.BN, tk = p.BK;
-  const int lda = tm + 1, ldb = tn + 1;
-  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  const int lda = tm + 4, ldb = tn + 4;  // rows stay 16-byte aligned for the vector reads
+  float* As = simt_smem;
+  float* Bs = simt_smem + tk * lda;
+  const int tm_shift = __ffs(tm) - 1, tn_shift = __ffs(tn) - 1, tk_shift = __ffs(tk) - 1;
+  // vector staging needs 16-byte (8-byte for 16-bit types) aligned rows: aligned bases and dimensions that are
+  // multiples of four elements (tile sizes are; the operands' leading dimensions are multiples of the tiles)
+  const bool vec = ((reinterpret_cast<uintptr_t>(p.A) | reinterpret_cast<uintptr_t>(p.B)) & 15) == 0;
+  const bool vec_c = (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
+  const int cols = tn / R;  // threads along N
+  const int ty = threadIdx.x / cols, tx = threadIdx.x - ty * cols;
 
   const int set = p.n_index_sets > 1 ? (p.mode == MODE_DDS ? blockIdx.y : blockIdx.z) : 0;
   const int32_t* ptr = p.ptr ? p.ptr + (long long)set * p.ptr_stride : nullptr;
@@ -91,11 +163,11 @@ __global__ void __launch_bounds__(kThreads) bsmm_simt_kernel(BsmmParams p) {
       chunk0 = ptr[line]; chunk1 = ptr[line + 1];
     }
 
-    float acc[4][4];
+    float acc[R][R];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < R; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+      for (int j = 0; j < R; ++j) acc[i][j] = 0.f;
 
     for (int t = chunk0; t < chunk1; ++t) {
       int kb = t, pos = t;
@@ -124,38 +196,43 @@ __global__ void __launch_bounds__(kThreads) bsmm_simt_kernel(BsmmParams p) {
         obp.s_outer = b_sn; obp.s_k = b_sk;
       }
       __syncthreads();
-      stage_tile<T>(As, oa, tm, tk, lda);
-      stage_tile<T>(Bs, obp, tn, tk, ldb);
+      stage_tile<T>(As, oa, tm, tk, lda, tm_shift, tk_shift, vec);
+      stage_tile<T>(Bs, obp, tn, tk, ldb, tn_shift, tk_shift, vec);
       __syncthreads();
+      const float* ap = As + ty * R;
+      const float* bp = Bs + tx * R;
 #pragma unroll 4
       for (int kk = 0; kk < tk; ++kk) {
-        float a[4], b[4];
+        float a[R], b[R];
+        load_frag<R>(ap + kk * lda, a);
+        load_frag<R>(bp + kk * ldb, b);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) a[i] = (ty + 16 * i < tm) ? As[kk * lda + ty + 16 * i] : 0.f;
+        for (int i = 0; i < R; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) b[j] = (tx + 16 * j < tn) ? Bs[kk * ldb + tx + 16 * j] : 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+          for (int j = 0; j < R; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
       }
     }
 
     // epilogue
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int m = ty + 16 * i;
-      if (m >= tm) continue;
+    for (int i = 0; i < R; ++i) {
+      const int m = ty * R + i;
+      T* crow = c_comp ? C + ((long long)c_pos * tm + m) * tn + tx * R
+                       : C + ((long long)by * tm + m) * p.N + (long long)bx * tn + tx * R;
+      alignas(16) T out[R];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int n = tx + 16 * j;
-        if (n >= tn) continue;
+      for (int j = 0; j < R; ++j) {
         float v = acc[i][j];
-        if (bias) v += to_float(bias[(long long)bx * tn + n]);
-        if (c_comp)
-          C[((long long)c_pos * tm + m) * tn + n] = from_float<T>(v);
-        else
-          C[((long long)by * tm + m) * p.N + (long long)bx * tn + n] = from_float<T>(v);
+        if (bias) v += to_float(bias[(long long)bx * tn + tx * R + j]);
+        out[j] = from_float<T>(v);
+      }
+      if (R > 1 && vec_c) {  // the thread's R outputs of a row as one store
+        if constexpr (R * sizeof(T) == 16) *reinterpret_cast<uint4*>(crow) = *reinterpret_cast<const uint4*>(out);
+        else if constexpr (R * sizeof(T) == 8) *reinterpret_cast<uint2*>(crow) = *reinterpret_cast<const uint2*>(out);
+        else if constexpr (R * sizeof(T) == 4) *reinterpret_cast<uint32_t*>(crow) = *reinterpret_cast<const uint32_t*>(out);
+      } else {
+#pragma unroll
+        for (int j = 0; j < R; ++j) crow[j] = out[j];
       }
     }
   }
@@ -163,6 +240,10 @@ __global__ void __launch_bounds__(kThreads) bsmm_simt_kernel(BsmmParams p) {
 
 template <typename T>
 int launch(const BsmmParams& p, cudaStream_t st) {
+  const int outputs = p.BM * p.BN;
+  const int r = outputs >= 1024 ? 4 : (outputs >= 256 ? 2 : 1);  // outputs per thread and dimension
+  const int threads = outputs / (r * r);                           // 64 .. 256 (16 for a 4 x 4 tile)
+  const size_t smem = (size_t)p.BK * (p.BM + 4 + p.BN + 4) * sizeof(float);  // at most 34 KB
   dim3 grid;
   if (p.mode == MODE_DDS) {
     long long gx = p.grid_blocks_hint > 0 ? p.grid_blocks_hint : (long long)(p.M / p.BM) * (p.N / p.BN);
@@ -172,7 +253,9 @@ int launch(const BsmmParams& p, cudaStream_t st) {
   } else {
     grid = dim3(p.N / p.BN, p.M / p.BM, p.batch);
   }
-  bsmm_simt_kernel<T><<<grid, kThreads, 0, st>>>(p);
+  if (r == 4) bsmm_simt_kernel<T, 4><<<grid, threads, smem, st>>>(p);
+  else if (r == 2) bsmm_simt_kernel<T, 2><<<grid, threads, smem, st>>>(p);
+  else bsmm_simt_kernel<T, 1><<<grid, threads, smem, st>>>(p);
   return launch_status();
 }
 
@@ -182,6 +265,7 @@ int bsmm_simt(const BsmmParams& p, cudaStream_t st) {
   if (dsd_fma_supported(p)) return dsd_fma_launch(p, st);
   if (p.BM > kMaxTile || p.BN > kMaxTile || p.BK > kMaxTile) return SPARTA_ERR_UNSUPPORTED;
   if (p.BM < 4 || p.BN < 4 || p.BK < 4) return SPARTA_ERR_UNSUPPORTED;
+  if ((p.BM & (p.BM - 1)) || (p.BN & (p.BN - 1)) || (p.BK & (p.BK - 1))) return SPARTA_ERR_UNSUPPORTED;  // powers of two
   if (p.batch > 65535 || p.M / p.BM > 65535) return SPARTA_ERR_SHAPE;
   switch (p.dtype) {
     case SPARTA_F32: return launch<float>(p, st);
