@@ -18,6 +18,8 @@
 //
 // Replaces sparta_sparse_matmul_dsd.cuh.j2 for these configurations (the reference covers 8 x 8 masks
 // with 16 x 16 or larger tiles, sparta/specializer/kernels/matmul.py:53-97).
+#include <type_traits>
+
 #include "bsmm.cuh"
 
 namespace sparta {
@@ -259,7 +261,7 @@ __global__ void __launch_bounds__(2 * TM) bsmm_dsd_fma_kernel(BsmmParams p) {
 // shared-memory pipe delivers at best, so the FMA pipe idled two thirds of the time.  Here a thread owns
 // 8 rows x (4 + 4) columns -- four columns in each of the panel's two block rows of W -- and per step of four
 // K values (eight for 16-bit types) reads 8 row pieces of X and 2 x 4 row pieces of W for 256 (512) multiply-adds:
-// one read per 16 (32).  Threads 0-127 take the first K-block of a chunk, threads 128-255 the second; a warp
+// one read per 16 (32).  Threads 0-127 and 128-255 share the kept blocks of a chunk between them; a warp
 // is 4 row groups x 8 column groups, so that every quarter warp reads one X address (broadcast) and eight W
 // rows whose 16-byte pieces are stored swizzled (piece q of row n at q ^ (n / 4)): no bank conflicts.
 // ---------------------------------------------------------------------------------------------------
@@ -375,21 +377,28 @@ __global__ void __launch_bounds__(256, Fma32Cfg<T>::kCtas) bsmm_dsd_fma32_kernel
     __syncthreads();
     if (c + kSt - 1 < n_chunks) issue(c + kSt - 1, (c + kSt - 1) % kSt);
     else asm volatile("cp.async.commit_group;" ::: "memory");
-    const uint32_t m = kmask[clist[c] * KC + g];  // the same for the 128 threads of a group
-    if (!m) continue;
+    // The chunk's kept (K-block, block row) products -- at most four -- are dealt out alternately to the two thread
+    // groups (whichever group computes a product, the partial sums are added at the end), starting with a
+    // different group every chunk: with one K-block per group, a chunk whose two K-blocks keep different numbers
+    // of blocks left one group waiting at the next barrier.
+    const int chunk = clist[c];
+    const uint32_t bits = (kmask[chunk * KC] & 3u) | ((kmask[chunk * KC + 1] & 3u) << 2);  // bit kc * 2 + l
     const uint8_t* xs = stage_mem + (c % kSt) * S::kStage;
     const uint8_t* ws = xs + S::kXBytes;
-    const T* xrow = reinterpret_cast<const T*>(xs + (ty * 8) * S::kXRow) + g * B;
-#pragma unroll 4
-    for (int q = 0; q < RP; ++q) {
-      float x[8][KV];
+    int turn = c + g;  // the product is this group's when `turn` is even
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        load_floats<T, KV>(reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(xrow) + i * S::kXRow) + q * KV, x[i]);
+    for (int pi = 0; pi < KC * P; ++pi) {
+      if (!((bits >> pi) & 1u)) continue;
+      if ((turn++) & 1) continue;
+      const int kc = pi >> 1, l = pi & 1;  // compile-time after unrolling: acc[l] stays in registers
+      const T* xrow = reinterpret_cast<const T*>(xs + (ty * 8) * S::kXRow) + kc * B;
+      const uint8_t* wb = ws + (kc * P + l) * (SP * 16);
+#pragma unroll 1
+      for (int q = 0; q < RP; ++q) {
+        float x[8][KV];
 #pragma unroll
-      for (int l = 0; l < P; ++l) {
-        if (!((m >> l) & 1u)) continue;
-        const uint8_t* wb = ws + (g * P + l) * (SP * 16);
+        for (int i = 0; i < 8; ++i)
+          load_floats<T, KV>(reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(xrow) + i * S::kXRow) + q * KV, x[i]);
         float w[4][KV];
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc)
