@@ -268,16 +268,19 @@ __global__ void __launch_bounds__(2 * TM) bsmm_dsd_fma_kernel(BsmmParams p) {
 // fp32: two stages and two CTAs per SM (102 KB each, 128 registers) measured 20 % faster than three stages and one
 // CTA (522 against 651 us on the dense 3072 x 768 x 4096 product); the 16-bit types need more registers for the
 // conversions and keep three stages, one CTA by registers.
-template <typename T>
+// Row tiles of 64 (128 threads, 67 KB, three CTAs per SM in fp32) serve token counts that are no multiple of 128;
+// where both apply the 128-row tile is faster even for small grids (notebook workload, 384 CTAs: 204 against
+// 235 us; dense grid point 531 against 624 us).
+template <typename T, int TM>
 struct Fma32Cfg {
   static constexpr int kStages = sizeof(T) == 4 ? 2 : 3;
-  static constexpr int kCtas = sizeof(T) == 4 ? 2 : 1;
+  static constexpr int kCtas = TM == 64 ? 3 : (sizeof(T) == 4 ? 2 : 1);
 };
 
-template <typename T>
-__global__ void __launch_bounds__(256, Fma32Cfg<T>::kCtas) bsmm_dsd_fma32_kernel(BsmmParams p) {
-  constexpr int B = 32, TM = 128, NT = 256, P = 2, KC = 2;
-  constexpr int kSt = Fma32Cfg<T>::kStages;
+template <typename T, int TM>
+__global__ void __launch_bounds__(2 * TM, Fma32Cfg<T, TM>::kCtas) bsmm_dsd_fma32_kernel(BsmmParams p) {
+  constexpr int B = 32, NT = 2 * TM, P = 2, KC = 2;
+  constexpr int kSt = Fma32Cfg<T, TM>::kStages;
   constexpr int KV = 16 / (int)sizeof(T);     // values per 16-byte piece
   constexpr int RP = B / KV;                  // pieces per block row (8 for fp32, 4 for 16-bit types)
   using S = FmaSmem<TM, T>;
@@ -359,7 +362,7 @@ __global__ void __launch_bounds__(256, Fma32Cfg<T>::kCtas) bsmm_dsd_fma32_kernel
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  const int g = threadIdx.x >> 7, t = threadIdx.x & 127, ty = t >> 3, tx = t & 7;
+  const int g = threadIdx.x / TM, t = threadIdx.x % TM, ty = t >> 3, tx = t & 7;
   float acc[P][8][4];
 #pragma unroll
   for (int l = 0; l < P; ++l)
@@ -417,14 +420,14 @@ __global__ void __launch_bounds__(256, Fma32Cfg<T>::kCtas) bsmm_dsd_fma32_kernel
 
   // the second group hands its partial sums over through the (now idle) staging memory: [value][thread]
   float* red = reinterpret_cast<float*>(stage_mem);
-  static_assert(kSt * S::kStage >= 128 * 64 * 4, "staging memory holds the partial sums");
+  static_assert(kSt * S::kStage >= TM * 64 * 4, "staging memory holds the partial sums");
   if (g == 1) {
 #pragma unroll
     for (int l = 0; l < P; ++l)
 #pragma unroll
       for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) red[((l * 8 + i) * 4 + c) * 128 + t] = acc[l][i][c];
+        for (int c = 0; c < 4; ++c) red[((l * 8 + i) * 4 + c) * TM + t] = acc[l][i][c];
   }
   __syncthreads();
   if (g == 1) return;
@@ -433,7 +436,7 @@ __global__ void __launch_bounds__(256, Fma32Cfg<T>::kCtas) bsmm_dsd_fma32_kernel
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) acc[l][i][c] += red[((l * 8 + i) * 4 + c) * 128 + t];
+      for (int c = 0; c < 4; ++c) acc[l][i][c] += red[((l * 8 + i) * 4 + c) * TM + t];
 
   // epilogue: + bias, convert; the eight threads of a row group write 32 consecutive columns of a row
   const T* bias = p.bias ? static_cast<const T*>(p.bias) + (long long)batch * p.N : nullptr;
@@ -458,16 +461,22 @@ __global__ void __launch_bounds__(256, Fma32Cfg<T>::kCtas) bsmm_dsd_fma32_kernel
   }
 }
 
-template <typename T>
-int launch_fma32(const BsmmParams& p, cudaStream_t st) {
-  using S = FmaSmem<128, T>;
-  auto kern = bsmm_dsd_fma32_kernel<T>;
+template <typename T, int TM>
+int launch_fma32_tm(const BsmmParams& p, cudaStream_t st) {
+  using S = FmaSmem<TM, T>;
+  auto kern = bsmm_dsd_fma32_kernel<T, TM>;
   static SmemAttrOnce attr;
-  constexpr int kSmem = Fma32Cfg<T>::kStages * S::kStage;
+  constexpr int kSmem = Fma32Cfg<T, TM>::kStages * S::kStage;
   if (cudaError_t e = attr.ensure(kern, kSmem); e != cudaSuccess) return static_cast<int>(e);
   const int panels = (p.N / 32 + 1) / 2;
-  kern<<<dim3(panels, p.M / 128, p.batch), 256, kSmem, st>>>(p);
+  kern<<<dim3(panels, p.M / TM, p.batch), 2 * TM, kSmem, st>>>(p);
   return launch_status();
+}
+
+template <typename T>
+int launch_fma32(const BsmmParams& p, cudaStream_t st) {
+  if (p.M % 128 == 0) return launch_fma32_tm<T, 128>(p, st);
+  return launch_fma32_tm<T, 64>(p, st);
 }
 
 template <int B, int TM, typename T>
@@ -494,7 +503,7 @@ int launch_t(const BsmmParams& p, cudaStream_t st) {
   switch (p.BN) {
     case 8: return launch_b<8, T>(p, st);
     case 16: return launch_b<16, T>(p, st);
-    case 32: return p.M % 128 == 0 ? launch_fma32<T>(p, st) : launch_b<32, T>(p, st);
+    case 32: return launch_fma32<T>(p, st);  // M is a multiple of 64 (dsd_fma_supported)
     default: return SPARTA_ERR_UNSUPPORTED;
   }
 }

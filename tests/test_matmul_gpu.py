@@ -286,3 +286,34 @@ def test_per_batch_masks_dds():
         torch.testing.assert_close(dense, full * masks.cpu().float(), **TOL[torch.float16])
         new = torch.stack([oracle.block_mask((M, N), (blk, blk), 0.8, generator=g) for _ in range(batch)])
         masks.copy_(new.cuda())  # rewritten in place: no update_mask call
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('M,K,N,sparsity', [
+    (128, 64, 32, 0.0),      # one row tile, one chunk, half a panel
+    (192, 256, 160, 0.5),    # 64-row tiles (192 is no multiple of 128), five block rows: the last panel holds one
+    (256, 1024, 320, 0.9),   # most chunks of a panel empty: they are neither fetched nor walked
+    (384, 512, 256, 1.0),    # a single block left: every other panel is bias only
+])
+def test_dsd_32x32_blocks_on_the_fma_units(dtype, M, K, N, sparsity):
+    """The register-tiled FMA kernel for 32 x 32 blocks (fp32 lives here; the 16-bit types reach it with _family='simt')."""
+    batch = 2
+    g = torch.Generator().manual_seed(M + K + N)
+    x = torch.randn((batch, M, K), generator=g).to(dtype)
+    w = (torch.randn((batch, N, K), generator=g) * 0.1).to(dtype)
+    b = torch.randn((batch, N), generator=g).to(dtype)
+    mask = oracle.block_mask((N, K), (32, 32), sparsity, generator=g)
+    if sparsity == 1.0:
+        mask.zero_()
+        mask[64:96, 128:160] = 1
+    w = w * mask
+    kernel = SparTASparseMatMulKernel(mode='dsd', biased=True, transpose_A=False, transpose_B=True, compressed=True)
+    kernel.ports['B'].set_mask(mask.cuda())
+    kernel.set_shape(batch, M, K, N)
+    kernel.compile({'_impl': 'sparta', '_family': 'simt', 'BLOCK_SIZE_M_VALUE': 64, 'BLOCK_SIZE_K_VALUE': 32,
+                    'BLOCK_SIZE_N_VALUE': 32})
+    ix = kernel.ports['B'].indexes
+    out = kernel(x.cuda(), ix.convert(w.cuda()), b.cuda())
+    expect = oracle.matmul_reference(x.float(), w.float(), b.float(), mask, 'dsd', False, True, (32, 32))
+    tol = TOL[dtype] if dtype != torch.float32 else dict(rtol=1e-4, atol=2e-4)  # sums over up to 1024 terms
+    torch.testing.assert_close(out.float().cpu(), expect, **tol)
