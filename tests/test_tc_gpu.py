@@ -300,3 +300,33 @@ def test_sparse_linear_trains_on_tcgen05(dtype):
     gw = op.get_sparse_indexes('B').inverse(op.weight.grad.unsqueeze(0)).squeeze(0)  # the weight is held compressed
     torch.testing.assert_close(gw.float().cpu(), wr.grad * mask, rtol=2e-2, atol=5e-2)
     torch.testing.assert_close(op.bias.grad.float().cpu(), br.grad, rtol=2e-2, atol=1e-1)
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('biased', [False, True])
+def test_dsd_tcgen05_panels_without_blocks(dtype, biased):
+    """Masks that leave whole panels of block rows empty (and one that is empty but for a single block): those
+    panels take the kernel's early exit and must come out as the bias (or zero)."""
+    batch, M, K, N = 2, 256, 512, 1024
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn((batch, M, K), generator=g).to(dtype)
+    w = (torch.randn((batch, N, K), generator=g) * 0.1).to(dtype)
+    b = torch.randn((batch, N), generator=g).to(dtype) if biased else None
+    for variant in range(2):
+        mask = torch.zeros((N, K), dtype=torch.uint8)
+        if variant == 0:
+            mask[640:672, 96:128] = 1            # a single block
+        else:
+            mask[:320] = oracle.block_mask((320, K), (32, 32), 0.7, generator=g)  # first panel(s) only
+        kernel = SparTASparseMatMulKernel(mode='dsd', biased=biased, transpose_A=False, transpose_B=True, compressed=True)
+        kernel.ports['B'].set_mask(mask.cuda())
+        kernel.set_shape(batch, M, K, N)
+        kernel.compile({'_impl': 'sparta', '_family': 'tcgen05', 'BLOCK_SIZE_M_VALUE': 128, 'BLOCK_SIZE_K_VALUE': 32,
+                        'BLOCK_SIZE_N_VALUE': 32})
+        ix = kernel.ports['B'].indexes
+        args = [x.cuda(), ix.convert((w * mask).cuda())] + ([b.cuda()] if biased else [])
+        out = kernel(*args)
+        assert _lib.last_status() == [0, 0, 0, 0]
+        expect = oracle.matmul_reference(x.float(), (w * mask).float(), b.float() if biased else None, mask, 'dsd',
+                                         False, True, (32, 32))
+        torch.testing.assert_close(out.float().cpu(), expect, **TOL)
