@@ -561,7 +561,11 @@ int attn_fwd_entry(const void* Q, const void* K, const void* V, void* O, const i
   if (D == 128 && attn_tc2_supported(Nt))
     return attn_tc2_launch(Q, K, V, O, row_ptr, bcsr_idx, mask, p.scale_log2, heads, Nt, Ns, D, dtype, lse, p.status,
                            copies, n_copies, st);
-  if (n_copies > 0) return SPARTA_ERR_UNSUPPORTED;  // the one-tile kernel stores O only
+  if (n_copies > 0) return SPARTA_ERR_UNSUPPORTED;  // the one-tile kernels store O only
+#ifndef SPARTA_ATTN64_TWO_BLOCKS
+  if (D == 64)
+    return attn_tc64_launch(Q, K, V, O, row_ptr, bcsr_idx, mask, p.scale_log2, heads, Nt, Ns, dtype, lse, p.status, st);
+#endif
   const int fmt = dtype == SPARTA_F16 ? 0 : 1;
   if (D == 64) return fmt == 0 ? launch_attn<64, 0>(Q, K, V, p, dtype, st) : launch_attn<64, 1>(Q, K, V, p, dtype, st);
   return fmt == 0 ? launch_attn<128, 0>(Q, K, V, p, dtype, st) : launch_attn<128, 1>(Q, K, V, p, dtype, st);

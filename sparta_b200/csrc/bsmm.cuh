@@ -47,6 +47,11 @@ int attn_tc2_launch(const void* Q, const void* K, const void* V, void* O, const 
                     const int32_t* bcsr_idx, const uint8_t* mask, float scale_log2, int heads, int Nt, int Ns,
                     int D, int dtype, float* lse, int32_t* status, void* const* copies, int n_copies, cudaStream_t st);
 
+// fused attention for head dim 64 with one K block per step and four CTAs per SM (attn_tc64.cu)
+int attn_tc64_launch(const void* Q, const void* K, const void* V, void* O, const int32_t* row_ptr,
+                     const int32_t* bcsr_idx, const uint8_t* mask, float scale_log2, int heads, int Nt, int Ns,
+                     int dtype, float* lse, int32_t* status, cudaStream_t st);
+
 // whether the tcgen05 matmul / fused attention kernels are compiled into this build
 bool bsmm_tc_available();
 bool attn_tc_available();
